@@ -1,0 +1,283 @@
+// The gated delta rule: a linear recurrence whose state is one matrix S [dim, vdim] per head,
+//     S <- g S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q
+// behind short causal convolutions (with silu) on the q, k and v projections, unit-length q and k,
+// a sigmoid step size beta and a decay g = exp(rate * softplus(a + dt_bias)) per head, and in front of
+// a head-wise RMS norm with a silu gate.
+//
+// The projection row of a token is [q (G*D) | k (G*D) | v (H*V) | gate (H*V) | b (H) | a (H) | ...]
+// in the run's dtype; everything behind it is 32-bit. Per sequence the state is one 32-bit row:
+// the convolution's last taps - 1 inputs [taps - 1, C] (C = 2 G D + H V, oldest first), then S [H, D, V].
+//
+// prepare  one block per token: convolution (state rows stand before the step's first token), silu,
+//          unit norms, beta, decay and k.q, into a 32-bit work row [qn | kn | v | beta | decay | kq (G)].
+// conv_state  the convolution's new last inputs; runs behind prepare, which reads the old ones.
+// scan     one block per (columns of S, head, sequence) walks the sequence's tokens in order. Every
+//          column of S is a recurrence of its own: a thread holds 16 elements of one column, DS threads
+//          a column; the two sums over dim use the state before the decay
+//          (S^T k after the decay is g times the sum before it, and o = g S^T q + u (k.q)), so both
+//          run as independent chains and are added over the DS threads by shuffles. Tokens are
+//          staged in shared memory eight at a time, the next eight requested under the current.
+// finish   o / sqrt(mean(o^2) + eps) * weight * silu(gate) per head, rounded to the run's dtype.
+#include "common.cuh"
+
+using namespace llmb;
+
+LLMB_DEFINE_LAST_ERROR(llmb_delta_rule)
+
+constexpr int THREADS = 256;
+constexpr int MAX_TAPS = 16;
+constexpr int DPT = 16;          // elements of a column a thread holds
+constexpr int CHUNK = 8;         // tokens staged at a time
+
+__device__ __forceinline__ float silu(float z) { return z / (1.0f + expf(-z)); }
+
+template <typename T>
+__global__ void __launch_bounds__(THREADS)
+delta_prepare_kernel(const T* __restrict__ proj, int ld, const float* __restrict__ taps, int n_taps,
+                     const float* __restrict__ state, long long state_stride, const int* __restrict__ tok_seq,
+                     const int* __restrict__ cu_seqlens, const int* __restrict__ slot_ids,
+                     const float* __restrict__ rate, const float* __restrict__ dt_bias, float unit_eps,
+                     float* __restrict__ work, int work_ld, int H, int G, int D, int V) {
+    extern __shared__ float row[];         // [C]
+    griddep_launch();
+    griddep_wait();
+    int t = blockIdx.x;
+    int seq = tok_seq[t];
+    int i = t - cu_seqlens[seq];
+    const float* st = state + (long long)slot_ids[seq] * state_stride;
+    int GD = G * D, C = 2 * GD + H * V;
+    for (int c = threadIdx.x; c < C; c += THREADS) {
+        float acc = 0.f;
+        for (int j = 0; j < n_taps; ++j) {
+            int d = n_taps - 1 - j;
+            float in = i - d >= 0 ? to_float(proj[(size_t)(t - d) * ld + c]) : st[(size_t)(n_taps - 1 - (d - i)) * C + c];
+            acc = fmaf(taps[(size_t)c * n_taps + j], in, acc);
+        }
+        row[c] = silu(acc);
+    }
+    __syncthreads();
+    float* out = work + (size_t)t * work_ld;
+    int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int g = warp; g < G; g += THREADS / 32) {
+        float sq = 0.f, sk = 0.f;
+        for (int d = lane; d < D; d += 32) {
+            float a = row[g * D + d], b = row[GD + g * D + d];
+            sq = fmaf(a, a, sq);
+            sk = fmaf(b, b, sk);
+        }
+        float rq = 1.0f / sqrtf(warp_sum(sq) + unit_eps) * (1.0f / sqrtf((float)D));
+        float rk = 1.0f / sqrtf(warp_sum(sk) + unit_eps);
+        float dot = 0.f;
+        for (int d = lane; d < D; d += 32) {
+            float a = row[g * D + d] * rq, b = row[GD + g * D + d] * rk;
+            out[g * D + d] = a;
+            out[GD + g * D + d] = b;
+            dot = fmaf(a, b, dot);
+        }
+        dot = warp_sum(dot);
+        if (lane == 0) out[C + 2 * H + g] = dot;
+    }
+    for (int e = threadIdx.x; e < H * V; e += THREADS) out[2 * GD + e] = row[2 * GD + e];
+    const T* in = proj + (size_t)t * ld + 2 * GD + 2 * H * V;
+    for (int a = threadIdx.x; a < H; a += THREADS) {
+        float b = to_float(in[a]);
+        out[C + a] = 1.0f / (1.0f + expf(-b));
+        float z = to_float(in[H + a]) + dt_bias[a];
+        float sp = z > 20.0f ? z : log1pf(expf(z));
+        out[C + H + a] = expf(rate[a] * sp);
+    }
+}
+
+template <typename T>
+__global__ void delta_conv_state_kernel(const T* __restrict__ proj, int ld, int n_taps, float* __restrict__ state,
+                                        long long state_stride, const int* __restrict__ cu_seqlens,
+                                        const int* __restrict__ slot_ids, int C) {
+    griddep_launch();
+    griddep_wait();
+    int c = blockIdx.x * blockDim.x + threadIdx.x, b = blockIdx.y;
+    if (c >= C) return;
+    int first = cu_seqlens[b], n = cu_seqlens[b + 1] - first;
+    if (n <= 0) return;
+    float* st = state + (long long)slot_ids[b] * state_stride;
+    float held[MAX_TAPS];
+    for (int r = 0; r < n_taps - 1; ++r) {
+        int src = n - (n_taps - 1) + r;
+        held[r] = src >= 0 ? to_float(proj[(size_t)(first + src) * ld + c]) : st[(size_t)(r + n) * C + c];
+    }
+    for (int r = 0; r < n_taps - 1; ++r) st[(size_t)r * C + c] = held[r];
+}
+
+__device__ __forceinline__ void copy4(float* smem, const float* global) {
+    unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(s), "l"(global));
+}
+
+// DS threads share a column (DS a power of two up to 32); a warp holds 32 / DS columns.
+__global__ void __launch_bounds__(THREADS)
+delta_scan_kernel(const float* __restrict__ work, int work_ld, float* __restrict__ state, long long state_stride,
+                  long long s_offset, const int* __restrict__ cu_seqlens, const int* __restrict__ slot_ids,
+                  float* __restrict__ out, int out_ld, int H, int G, int D, int V, int DS) {
+    extern __shared__ float stage[];       // two buffers of [CHUNK] x (q [Dp] | k [Dp] | v [VC] | beta, decay, kq, pad)
+    griddep_launch();
+    int a = blockIdx.y, b = blockIdx.z;
+    int g = a / (H / G);
+    int Dp = DS * DPT, VC = THREADS / DS;
+    int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int slice = lane % DS;
+    int col = blockIdx.x * VC + warp * (32 / DS) + lane / DS;
+    int local_col = col - blockIdx.x * VC;
+    int per_token = 2 * Dp + VC + 4, buffer = CHUNK * per_token;
+    int GD = G * D, C = 2 * GD + H * V;
+    griddep_wait();
+    int first = cu_seqlens[b], n = cu_seqlens[b + 1] - first;
+    if (n <= 0) return;
+    float* S_global = state + (long long)slot_ids[b] * state_stride + s_offset + (size_t)a * D * V;
+    float S[DPT];
+#pragma unroll
+    for (int e = 0; e < DPT; ++e) {
+        int d = slice * DPT + e;
+        S[e] = (d < D && col < V) ? S_global[(size_t)d * V + col] : 0.f;
+    }
+    // the padding of q and k beyond D stays zero in both buffers
+    for (int i = threadIdx.x; i < 2 * buffer; i += THREADS) stage[i] = 0.f;
+    __syncthreads();
+    auto request = [&](int chunk, float* buf) {
+        int base = chunk * CHUNK;
+        int count = min(CHUNK, n - base);
+        for (int i = threadIdx.x; i < count * per_token; i += THREADS) {
+            int tt = i / per_token, e = i % per_token;
+            const float* src = work + (size_t)(first + base + tt) * work_ld;
+            float* dst = buf + tt * per_token + e;
+            if (e < Dp) { if (e < D) copy4(dst, src + g * D + e); }
+            else if (e < 2 * Dp) { if (e - Dp < D) copy4(dst, src + GD + g * D + (e - Dp)); }
+            else if (e < 2 * Dp + VC) {
+                int j = blockIdx.x * VC + (e - 2 * Dp);
+                if (j < V) copy4(dst, src + 2 * GD + a * V + j);
+            } else {
+                int which = e - 2 * Dp - VC;
+                if (which == 0) copy4(dst, src + C + a);
+                else if (which == 1) copy4(dst, src + C + H + a);
+                else if (which == 2) copy4(dst, src + C + 2 * H + g);
+            }
+        }
+        asm volatile("cp.async.commit_group;\n" ::);
+    };
+    int n_chunks = (n + CHUNK - 1) / CHUNK;
+    request(0, stage);
+    for (int chunk = 0; chunk < n_chunks; ++chunk) {
+        float* buf = stage + (chunk & 1) * buffer;
+        if (chunk + 1 < n_chunks) {
+            request(chunk + 1, stage + ((chunk + 1) & 1) * buffer);
+            asm volatile("cp.async.wait_group 1;\n" ::);
+        } else {
+            asm volatile("cp.async.wait_group 0;\n" ::);
+        }
+        __syncthreads();
+        int count = min(CHUNK, n - chunk * CHUNK);
+        for (int tt = 0; tt < count; ++tt) {
+            const float* tok = buf + tt * per_token;
+            const float4* q4 = reinterpret_cast<const float4*>(tok + slice * DPT);
+            const float4* k4 = reinterpret_cast<const float4*>(tok + Dp + slice * DPT);
+            float k[DPT];
+            float sk = 0.f, sq = 0.f;
+#pragma unroll
+            for (int e = 0; e < DPT / 4; ++e) {
+                float4 kv = k4[e], qv = q4[e];
+                k[4 * e] = kv.x; k[4 * e + 1] = kv.y; k[4 * e + 2] = kv.z; k[4 * e + 3] = kv.w;
+                sk = fmaf(S[4 * e], kv.x, sk); sq = fmaf(S[4 * e], qv.x, sq);
+                sk = fmaf(S[4 * e + 1], kv.y, sk); sq = fmaf(S[4 * e + 1], qv.y, sq);
+                sk = fmaf(S[4 * e + 2], kv.z, sk); sq = fmaf(S[4 * e + 2], qv.z, sq);
+                sk = fmaf(S[4 * e + 3], kv.w, sk); sq = fmaf(S[4 * e + 3], qv.w, sq);
+            }
+            for (int offset = DS >> 1; offset > 0; offset >>= 1) {
+                sk += __shfl_xor_sync(0xffffffffu, sk, offset);
+                sq += __shfl_xor_sync(0xffffffffu, sq, offset);
+            }
+            float v = tok[2 * Dp + local_col];
+            float beta = tok[2 * Dp + VC], decay = tok[2 * Dp + VC + 1], kq = tok[2 * Dp + VC + 2];
+            float u = beta * (v - decay * sk);
+            float o = fmaf(u, kq, decay * sq);
+#pragma unroll
+            for (int e = 0; e < DPT; ++e) S[e] = fmaf(k[e], u, decay * S[e]);
+            if (slice == 0 && col < V) out[(size_t)(first + chunk * CHUNK + tt) * out_ld + a * V + col] = o;
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int e = 0; e < DPT; ++e) {
+        int d = slice * DPT + e;
+        if (d < D && col < V) S_global[(size_t)d * V + col] = S[e];
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(THREADS)
+delta_finish_kernel(const float* __restrict__ o, int o_ld, const T* __restrict__ gate, int gate_ld,
+                    const float* __restrict__ weight, float eps, T* __restrict__ mixed, int mixed_ld, int H, int V) {
+    griddep_launch();
+    griddep_wait();
+    size_t t = blockIdx.x;
+    int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int a = warp; a < H; a += THREADS / 32) {
+        const float* row = o + t * o_ld + a * V;
+        float sq = 0.f;
+        for (int j = lane; j < V; j += 32) sq = fmaf(row[j], row[j], sq);
+        float rstd = 1.0f / sqrtf(warp_sum(sq) / (float)V + eps);
+        for (int j = lane; j < V; j += 32) {
+            float z = to_float(gate[t * gate_ld + a * V + j]);
+            mixed[t * mixed_ld + a * V + j] = from_float<T>(row[j] * rstd * weight[j] * silu(z));
+        }
+    }
+}
+
+// proj [T, ld] in `dtype`; taps float32 [C, n_taps]; state float32 [slots, state_stride] (conv rows, then S);
+// work float32 [T, work_ld >= C + 2 H + G]; o float32 [T, H V]; mixed [T, mixed_ld] in `dtype`.
+LLMB_EXPORT int llmb_delta_rule(const void* proj, int ld, int dtype, const float* taps, int n_taps, float* state,
+                                long long state_stride, const int* tok_seq, const int* cu_seqlens, const int* slot_ids,
+                                const float* rate, const float* dt_bias, float unit_eps, const float* norm_weight,
+                                float eps, float* work, int work_ld, float* o, void* mixed, int mixed_ld, int n_tokens,
+                                int n_seqs, int H, int G, int D, int V, cudaStream_t stream) {
+    if (n_tokens == 0) return LLMB_OK;
+    LLMB_REQUIRE(H > 0 && G > 0 && H % G == 0 && D > 0 && V > 0, "delta_rule: bad head sizes %d / %d / %d / %d", H, G, D, V);
+    LLMB_REQUIRE(n_taps >= 1 && n_taps <= MAX_TAPS, "delta_rule: %d taps (1 to %d are built)", n_taps, MAX_TAPS);
+    LLMB_REQUIRE(D <= 32 * DPT, "delta_rule: a key size of %d (up to %d is built)", D, 32 * DPT);
+    int C = 2 * G * D + H * V;
+    LLMB_REQUIRE(ld >= C + H * V + 2 * H && work_ld >= C + 2 * H + G, "delta_rule: rows too narrow");
+    LLMB_REQUIRE(state_stride >= (long long)(n_taps - 1) * C + (long long)H * D * V, "delta_rule: state too small");
+    LLMB_REQUIRE(work_ld % 1 == 0 && ((size_t)work % 4) == 0, "delta_rule: misaligned work rows");
+    int DS = 1;
+    while (DS * DPT < D) DS *= 2;
+    int VC = THREADS / DS;
+    size_t smem_row = sizeof(float) * (size_t)C;
+    size_t smem_scan = sizeof(float) * 2 * CHUNK * (size_t)(2 * DS * DPT + VC + 4);
+    LLMB_REQUIRE(smem_row <= 200 * 1024, "delta_rule: a row of %d channels does not fit in shared memory", C);
+    dim3 scan_grid((V + VC - 1) / VC, H, n_seqs);
+    long long s_offset = (long long)(n_taps - 1) * C;
+#define LLMB_DELTA(T)                                                                                              \
+    do {                                                                                                           \
+        if (smem_row > 48 * 1024)                                                                                  \
+            LLMB_CUDA(cudaFuncSetAttribute(delta_prepare_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,   \
+                                           (int)smem_row));                                                        \
+        LLMB_CUDA(llmb::launch(delta_prepare_kernel<T>, dim3(n_tokens), dim3(THREADS), smem_row, stream, true,     \
+                               (const T*)proj, ld, taps, n_taps, (const float*)state, state_stride, tok_seq,       \
+                               cu_seqlens, slot_ids, rate, dt_bias, unit_eps, work, work_ld, H, G, D, V));         \
+        if (n_taps > 1)                                                                                            \
+            LLMB_CUDA(llmb::launch(delta_conv_state_kernel<T>, dim3((C + 127) / 128, n_seqs), dim3(128), 0, stream, \
+                                   true, (const T*)proj, ld, n_taps, state, state_stride, cu_seqlens, slot_ids, C)); \
+        LLMB_CUDA(llmb::launch(delta_scan_kernel, scan_grid, dim3(THREADS), smem_scan, stream, true,               \
+                               (const float*)work, work_ld, state, state_stride, s_offset, cu_seqlens, slot_ids,  \
+                               o, H * V, H, G, D, V, DS));                                                         \
+        LLMB_CUDA(llmb::launch(delta_finish_kernel<T>, dim3(n_tokens), dim3(THREADS), 0, stream, true,             \
+                               (const float*)o, H * V, (const T*)proj + C, ld, norm_weight, eps, (T*)mixed,        \
+                               mixed_ld, H, V));                                                                   \
+    } while (0)
+    if (dtype == LLMB_DTYPE_F32) LLMB_DELTA(float);
+    else if (dtype == LLMB_DTYPE_BF16) LLMB_DELTA(__nv_bfloat16);
+    else return fail(LLMB_ERR_ARGUMENT, "delta_rule: unknown dtype %d", dtype);
+#undef LLMB_DELTA
+    return check_launch("delta_rule");
+}
+LLMB_PACKED(llmb_delta_rule)
+
+// launches of one call (for the caller's count)
+LLMB_EXPORT int llmb_delta_rule_launches(int n_taps) { return n_taps > 1 ? 4 : 3; }

@@ -37,7 +37,7 @@ norm_rope_cache_write_kernel(const T* __restrict__ u, int u_stride, int q_width,
                              const int* __restrict__ tok_pos, const int* __restrict__ tok_seq, T* __restrict__ q_out,
                              int q_out_stride, const int* __restrict__ block_table, int table_stride, int ring_pages,
                              T* __restrict__ k_cache, int k_heads, T* __restrict__ v_cache, int v_heads,
-                             int write_cache) {
+                             int write_cache, int v_source) {
     extern __shared__ float row[];         // [q_width + k_width]
     __shared__ float scratch[THREADS / 32];
     griddep_launch();
@@ -93,7 +93,7 @@ norm_rope_cache_write_kernel(const T* __restrict__ u, int u_stride, int q_width,
     }
     if (write_cache && v_width > 0) {
         int v_dim = v_width / v_heads;
-        const T* values = in + q_width + k_width;
+        const T* values = in + v_source;       // as projected: a source inside the key columns gives the keys before rotation
         for (int e = threadIdx.x; e < v_width; e += THREADS) {
             int head = e / v_dim, d = e % v_dim;
             v_cache[((page * v_heads + head) * LLMB_PAGE + slot_row) * v_dim + d] = values[e];
@@ -102,12 +102,15 @@ norm_rope_cache_write_kernel(const T* __restrict__ u, int u_stride, int q_width,
 }
 
 // k_cache [pages, k_heads, 64, k_width / k_heads], v_cache [pages, v_heads, 64, v_width / v_heads] (v_width == 0: none).
+// The values of a token are the v_width columns of u from column v_source on (q_width + k_width: the columns behind
+// the keys; q_width: the keys themselves as projected, for a mixer without a value projection).
 LLMB_EXPORT int llmb_norm_rope_cache_write(const void* u, int u_stride, int dtype, int q_width, int k_width, int v_width,
                                            const float* q_gain, const float* k_gain, float eps, const float* rope_table,
                                            int n_rot, int rot_unit, int interleaved, const int* tok_pos,
                                            const int* tok_seq, void* q_out, int q_out_stride, const int* block_table,
                                            int table_stride, int ring_pages, void* k_cache, int k_heads, void* v_cache,
-                                           int v_heads, int write_cache, int n_tokens, cudaStream_t stream) {
+                                           int v_heads, int write_cache, int v_source, int n_tokens,
+                                           cudaStream_t stream) {
     if (n_tokens == 0) return LLMB_OK;
     LLMB_REQUIRE(q_width > 0 && k_width > 0 && v_width >= 0 && k_heads > 0 && k_width % k_heads == 0,
                  "norm_rope_cache_write: bad widths %d / %d / %d with %d key heads", q_width, k_width, v_width, k_heads);
@@ -117,6 +120,7 @@ LLMB_EXPORT int llmb_norm_rope_cache_write(const void* u, int u_stride, int dtyp
                                  k_width % rot_unit == 0),
                  "norm_rope_cache_write: %d rotated elements do not fit units of %d", n_rot, rot_unit);
     LLMB_REQUIRE(ring_pages > 0, "norm_rope_cache_write: no pages");
+    LLMB_REQUIRE(v_source >= 0, "norm_rope_cache_write: the values start at column %d", v_source);
     size_t smem = sizeof(float) * (size_t)(q_width + k_width);
     LLMB_REQUIRE(smem <= 200 * 1024, "norm_rope_cache_write: a row of %d + %d values does not fit in shared memory",
                  q_width, k_width);
@@ -129,7 +133,7 @@ LLMB_EXPORT int llmb_norm_rope_cache_write(const void* u, int u_stride, int dtyp
                                (const T*)u, u_stride, q_width, k_width, v_width, q_gain, k_gain, eps, rope_table,   \
                                rope_table ? n_rot : 0, rot_unit > 0 ? rot_unit : 1, interleaved, tok_pos, tok_seq,   \
                                (T*)q_out, q_out_stride, block_table, table_stride, ring_pages, (T*)k_cache, k_heads, \
-                               (T*)v_cache, v_heads, write_cache));                                                  \
+                               (T*)v_cache, v_heads, write_cache, v_source));                                        \
     } while (0)
     if (dtype == LLMB_DTYPE_F32) LLMB_NORM_ROPE(float);
     else if (dtype == LLMB_DTYPE_BF16) LLMB_NORM_ROPE(__nv_bfloat16);

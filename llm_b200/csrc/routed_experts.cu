@@ -1,0 +1,381 @@
+// A feed-forward of routed experts: every token is sent to the `top` experts with the largest router
+// logits, its result is the sum of their results weighted by the softmax over the chosen logits.
+//
+// router   one block per token: logits = W_r h + b in 32-bit (W_r and b are held in 32-bit; h is the
+//          normed input in the run's dtype), the `top` largest (the lower index wins a tie), softmax over
+//          them. An assignment is a pair (token, k): index t * top + k.
+// plan     one block: counts the assignments of every expert, lists them grouped by expert (inside an
+//          expert in rising order, so the plan is a function of the routing alone) and cuts every
+//          expert's list into tiles of TILE_M rows: (expert, first row, rows) per tile. Nothing of this
+//          reaches the host: the product kernels are launched with the largest possible tile count
+//          and blocks beyond the plan's count leave at once, so a step can be captured and replayed.
+// up       for every tile: act[s, :] = silu(W_gate,e h_t) * (W_up,e h_t) for the rows s of the sorted list
+//          (h_t gathered through the list), one weight matrix [2 F, K] per expert (gate rows, then up).
+// down     for every tile: y[t * top + k, :] = weight[t, k] * (W_down,e act[s, :]), 32-bit, written at the
+//          assignment's own index; the sum over k is taken by the kernel behind (fixed order).
+// Every output element is one sum over K in rising order, whatever else is in its tile: results do
+// not depend on the batch.
+//
+// Two forms of the products: CUDA cores (any dtype, 32 x 64 tiles) and, for bfloat16 with K % 16 == 0,
+// mma.sync tiles with 32-bit accumulation.
+#include "common.cuh"
+#include "mma.cuh"
+
+using namespace llmb;
+
+LLMB_DEFINE_LAST_ERROR(llmb_routed_experts)
+
+constexpr int MAX_TOP = 16;
+constexpr int TILE_M = 32;
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+router_kernel(const T* __restrict__ h, int ld, const float* __restrict__ w, const float* __restrict__ bias,
+              int hidden, int E, int top, int* __restrict__ ids, float* __restrict__ weights) {
+    extern __shared__ float logits[];      // [E]
+    griddep_launch();
+    griddep_wait();
+    size_t t = blockIdx.x;
+    int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int e = warp; e < E; e += 4) {
+        float acc = 0.f;
+        for (int c = lane; c < hidden; c += 32) acc = fmaf(w[(size_t)e * hidden + c], to_float(h[t * ld + c]), acc);
+        acc = warp_sum(acc);
+        if (lane == 0) logits[e] = acc + (bias ? bias[e] : 0.f);
+    }
+    __syncthreads();
+    if (threadIdx.x != 0) return;
+    float chosen[MAX_TOP];
+    for (int k = 0; k < top; ++k) {
+        int best = 0;
+        float value = -INFINITY;
+        for (int e = 0; e < E; ++e)
+            if (logits[e] > value) { value = logits[e]; best = e; }
+        chosen[k] = value;
+        ids[t * top + k] = best;
+        logits[best] = -INFINITY;
+    }
+    float total = 0.f, largest = chosen[0];
+    for (int k = 0; k < top; ++k) { chosen[k] = expf(chosen[k] - largest); total += chosen[k]; }
+    for (int k = 0; k < top; ++k) weights[t * top + k] = chosen[k] / total;
+}
+
+// plan: [0, E] offsets | [E + 1] tile count | then three arrays of max_tiles: expert, first row, rows
+__global__ void __launch_bounds__(1024)
+plan_kernel(const int* __restrict__ ids, int n_assign, int E, int* __restrict__ sorted, int* __restrict__ plan,
+            int max_tiles) {
+    extern __shared__ int shared[];        // counts [E] | offsets [E + 1] | tile bases [E + 1]
+    int* counts = shared;
+    int* offsets = shared + E;
+    int* bases = shared + 2 * E + 1;
+    griddep_launch();
+    griddep_wait();
+    int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+    for (int e = warp; e < E; e += n_warps) {
+        int count = 0;
+        for (int i = lane; i < n_assign; i += 32) count += ids[i] == e;
+        for (int offset = 16; offset > 0; offset >>= 1) count += __shfl_xor_sync(0xffffffffu, count, offset);
+        if (lane == 0) counts[e] = count;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0, tiles = 0;
+        for (int e = 0; e < E; ++e) {
+            offsets[e] = at;
+            bases[e] = tiles;
+            at += counts[e];
+            tiles += (counts[e] + TILE_M - 1) / TILE_M;
+        }
+        offsets[E] = at;
+        bases[E] = tiles;
+        plan[E + 1] = tiles < max_tiles ? tiles : max_tiles;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e <= E; e += blockDim.x) plan[e] = offsets[e];
+    int* tile_expert = plan + E + 2;
+    int* tile_first = tile_expert + max_tiles;
+    int* tile_rows = tile_first + max_tiles;
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        int n = counts[e];
+        for (int i = 0, tile = bases[e]; i < n && tile < max_tiles; i += TILE_M, ++tile) {
+            tile_expert[tile] = e;
+            tile_first[tile] = offsets[e] + i;
+            tile_rows[tile] = min(TILE_M, n - i);
+        }
+    }
+    const unsigned below = (1u << lane) - 1u;
+    for (int e = warp; e < E; e += n_warps) {
+        int at = offsets[e];
+        for (int i0 = 0; i0 < n_assign; i0 += 32) {
+            int i = i0 + lane;
+            bool mine = i < n_assign && ids[i] == e;
+            unsigned mask = __ballot_sync(0xffffffffu, mine);
+            if (mine) sorted[at + __popc(mask & below)] = i;
+            at += __popc(mask);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------- CUDA cores
+
+constexpr int BN = 64, BK = 16;
+
+// GLU: W is [2 N, K] per expert (gate rows, then up rows), the result silu(gate) * up in T.
+// else: the result weight[row] * sum in 32-bit at row `sorted[s]` of y.
+template <typename T, bool GLU>
+__global__ void __launch_bounds__(256)
+expert_product_kernel(const T* __restrict__ A, int lda, int a_div, const T* __restrict__ W, long long w_stride, int N,
+                      int K, const int* __restrict__ sorted, const int* __restrict__ plan, int E, int max_tiles,
+                      T* __restrict__ act, float* __restrict__ y, const float* __restrict__ weights) {
+    __shared__ float As[BK][TILE_M + 1];
+    __shared__ float Bs[GLU ? 2 : 1][BK][BN + 1];
+    griddep_launch();
+    griddep_wait();
+    int tile = blockIdx.y;
+    if (tile >= plan[E + 1]) return;
+    const int* tile_expert = plan + E + 2;
+    int e = tile_expert[tile], first = tile_expert[max_tiles + tile], rows = tile_expert[2 * max_tiles + tile];
+    const T* We = W + (long long)e * w_stride;
+    int n0 = blockIdx.x * BN;
+    int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    float acc[GLU ? 2 : 1][2][4] = {};
+    // which row of A a thread loads: two elements of the 32 x 16 tile
+    int a_row = threadIdx.x >> 3, a_k = (threadIdx.x & 7) * 2;
+    long long a_src = -1;
+    if (a_row < rows) a_src = GLU ? (long long)(sorted[first + a_row] / a_div) * lda : (long long)(first + a_row) * lda;
+    for (int k0 = 0; k0 < K; k0 += BK) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            int k = k0 + a_k + i;
+            As[a_k + i][a_row] = (a_src >= 0 && k < K) ? to_float(A[a_src + k]) : 0.f;
+        }
+#pragma unroll
+        for (int half = 0; half < (GLU ? 2 : 1); ++half)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                int idx = threadIdx.x + i * 256;          // 64 x 16 elements
+                int n = idx >> 4, kk = idx & 15;
+                int col = n0 + n, k = k0 + kk;
+                Bs[half][kk][n] = (col < N && k < K) ? to_float(We[(long long)(half * N + col) * K + k]) : 0.f;
+            }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < BK; ++kk) {
+            float a[2] = {As[kk][ty * 2], As[kk][ty * 2 + 1]};
+#pragma unroll
+            for (int half = 0; half < (GLU ? 2 : 1); ++half)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    float b = Bs[half][kk][tx * 4 + j];
+                    acc[half][0][j] = fmaf(a[0], b, acc[half][0][j]);
+                    acc[half][1][j] = fmaf(a[1], b, acc[half][1][j]);
+                }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        int r = ty * 2 + i;
+        if (r >= rows) continue;
+        int s = first + r;
+        if (GLU) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                int col = n0 + tx * 4 + j;
+                if (col < N) {
+                    float g = acc[0][i][j];
+                    act[(long long)s * N + col] = from_float<T>(g / (1.0f + expf(-g)) * acc[GLU ? 1 : 0][i][j]);
+                }
+            }
+        } else {
+            int assignment = sorted[s];
+            float wgt = weights[assignment];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                int col = n0 + tx * 4 + j;
+                if (col < N) y[(long long)assignment * N + col] = wgt * acc[0][i][j];
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------- tensor cores
+
+// 32 rows x 128 columns a block of four warps (a warp: 32 x 32), k in steps of 32 through shared memory
+// (cp.async, two stages); for GLU the 128 columns are 64 gate and the 64 up columns of the same features.
+constexpr int TC_BN = 128, TC_BK = 32, TC_LD = TC_BK + 8;
+
+template <bool GLU>
+__global__ void __launch_bounds__(128)
+expert_product_tc_kernel(const __nv_bfloat16* __restrict__ A, int lda, int a_div, const __nv_bfloat16* __restrict__ W,
+                         long long w_stride, int N, int K, const int* __restrict__ sorted, const int* __restrict__ plan,
+                         int E, int max_tiles, __nv_bfloat16* __restrict__ act, float* __restrict__ y,
+                         const float* __restrict__ weights) {
+    __shared__ __align__(16) __nv_bfloat16 As[2][TILE_M][TC_LD];
+    __shared__ __align__(16) __nv_bfloat16 Bs[2][TC_BN][TC_LD];
+    griddep_launch();
+    griddep_wait();
+    int tile = blockIdx.y;
+    if (tile >= plan[E + 1]) return;
+    const int* tile_expert = plan + E + 2;
+    int e = tile_expert[tile], first = tile_expert[max_tiles + tile], rows = tile_expert[2 * max_tiles + tile];
+    const __nv_bfloat16* We = W + (long long)e * w_stride;
+    constexpr int FEATURES = GLU ? TC_BN / 2 : TC_BN;      // output features a block covers
+    int n0 = blockIdx.x * FEATURES;
+    int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // loads: A 32 rows x 4 pieces of 8 = 128 pieces, one a thread; B 128 rows x 4 pieces = 512, four a thread
+    int a_row = threadIdx.x >> 2, a_piece = (threadIdx.x & 3) * 8;
+    const __nv_bfloat16* a_src = nullptr;
+    if (a_row < rows)
+        a_src = A + (GLU ? (long long)(sorted[first + a_row] / a_div) * lda : (long long)(first + a_row) * lda);
+    auto request = [&](int stage, int k0) {
+        if (a_src) cp_async16(&As[stage][a_row][a_piece], a_src + k0 + a_piece);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            int idx = threadIdx.x + i * 128;
+            int n = idx >> 2, piece = (idx & 3) * 8;
+            int feature = GLU ? n0 + (n & 63) : n0 + n;
+            long long w_row = GLU ? (long long)((n >> 6) * N + feature) : (long long)feature;
+            if (feature < N) cp_async16(&Bs[stage][n][piece], We + w_row * K + k0 + piece);
+        }
+        cp_async_commit();
+    };
+    // rows and columns that are never loaded must read as zeros
+    for (int i = threadIdx.x; i < 2 * TILE_M * TC_LD; i += 128) (&As[0][0][0])[i] = __float2bfloat16(0.f);
+    for (int i = threadIdx.x; i < 2 * TC_BN * TC_LD; i += 128) (&Bs[0][0][0])[i] = __float2bfloat16(0.f);
+    __syncthreads();
+    float acc[2][4][4] = {};               // [row block of 16][column block of 8][fragment]
+    int n_k = K / TC_BK;
+    request(0, 0);
+    for (int kb = 0; kb < n_k; ++kb) {
+        int stage = kb & 1;
+        if (kb + 1 < n_k) { request(stage ^ 1, (kb + 1) * TC_BK); cp_async_wait<1>(); }
+        else cp_async_wait<0>();
+        __syncthreads();
+#pragma unroll
+        for (int ks = 0; ks < TC_BK; ks += 16) {
+            uint32_t a[2][4], b[2][4];
+#pragma unroll
+            for (int mi = 0; mi < 2; ++mi)
+                ldmatrix_x4(a[mi], &As[stage][mi * 16 + (lane & 15)][ks + (lane >> 4) * 8]);
+#pragma unroll
+            for (int ni = 0; ni < 2; ++ni)       // 16 columns each: two 8-column blocks x two k halves
+                ldmatrix_x4(b[ni], &Bs[stage][warp * 32 + ni * 16 + (lane & 7) + ((lane >> 4) << 3)][ks + ((lane >> 3) & 1) * 8]);
+#pragma unroll
+            for (int mi = 0; mi < 2; ++mi)
+#pragma unroll
+                for (int ni = 0; ni < 2; ++ni) {
+                    mma_bf16(acc[mi][ni * 2], a[mi][0], a[mi][1], a[mi][2], a[mi][3], b[ni][0], b[ni][1]);
+                    mma_bf16(acc[mi][ni * 2 + 1], a[mi][0], a[mi][1], a[mi][2], a[mi][3], b[ni][2], b[ni][3]);
+                }
+        }
+        __syncthreads();
+    }
+    // accumulator element (mi, nj, f): row mi * 16 + lane / 4 + (f / 2) * 8, column warp * 32 + nj * 8 + (lane % 4) * 2 + f % 2
+    if (GLU) {
+        // gate columns live in warps 0-1, up columns in warps 2-3: exchanged through shared memory
+        __shared__ float up[TILE_M][64 + 1];
+        if (warp >= 2)
+#pragma unroll
+            for (int mi = 0; mi < 2; ++mi)
+#pragma unroll
+                for (int nj = 0; nj < 4; ++nj)
+#pragma unroll
+                    for (int f = 0; f < 4; ++f)
+                        up[mi * 16 + (lane >> 2) + (f >> 1) * 8][(warp - 2) * 32 + nj * 8 + (lane & 3) * 2 + (f & 1)] = acc[mi][nj][f];
+        __syncthreads();
+        if (warp < 2)
+#pragma unroll
+            for (int mi = 0; mi < 2; ++mi)
+#pragma unroll
+                for (int nj = 0; nj < 4; ++nj)
+#pragma unroll
+                    for (int f = 0; f < 4; ++f) {
+                        int r = mi * 16 + (lane >> 2) + (f >> 1) * 8;
+                        int c = warp * 32 + nj * 8 + (lane & 3) * 2 + (f & 1);
+                        int feature = n0 + c;
+                        if (r < rows && feature < N) {
+                            float g = acc[mi][nj][f];
+                            act[(long long)(first + r) * N + feature] = __float2bfloat16_rn(g / (1.0f + expf(-g)) * up[r][c]);
+                        }
+                    }
+    } else {
+#pragma unroll
+        for (int mi = 0; mi < 2; ++mi)
+#pragma unroll
+            for (int f2 = 0; f2 < 2; ++f2) {
+                int r = mi * 16 + (lane >> 2) + f2 * 8;
+                if (r >= rows) continue;
+                int assignment = sorted[first + r];
+                float wgt = weights[assignment];
+#pragma unroll
+                for (int nj = 0; nj < 4; ++nj)
+#pragma unroll
+                    for (int f = 0; f < 2; ++f) {
+                        int col = n0 + warp * 32 + nj * 8 + (lane & 3) * 2 + f;
+                        if (col < N) y[(long long)assignment * N + col] = wgt * acc[mi][nj][f2 * 2 + f];
+                    }
+            }
+    }
+}
+
+LLMB_EXPORT long long llmb_routed_experts_plan_ints(int n_tokens, int top, int E) {
+    long long max_tiles = ((long long)n_tokens * top + TILE_M - 1) / TILE_M + E;
+    return (long long)E + 2 + 3 * max_tiles;
+}
+
+// h [T, ld] in `dtype`; router float32 [E, hidden] and bias float32 [E] (or null); w_up [E, 2 F, hidden] (gate rows,
+// then up rows) and w_down [E, hidden, F] in `dtype`; ids int32 [T * top], weights float32 [T * top], sorted
+// int32 [T * top], plan int32 [plan_ints]; act [T * top, F] in `dtype`; y float32 [T * top, hidden].
+LLMB_EXPORT int llmb_routed_experts(const void* h, int ld, int dtype, const float* router, const float* router_bias,
+                                    const void* w_up, const void* w_down, int* ids, float* weights, int* sorted,
+                                    int* plan, void* act, float* y, int n_tokens, int hidden, int F, int E, int top,
+                                    int tensor_cores, cudaStream_t stream) {
+    if (n_tokens == 0) return LLMB_OK;
+    LLMB_REQUIRE(hidden > 0 && F > 0 && E > 0 && top > 0 && top <= E && top <= MAX_TOP,
+                 "routed_experts: %d of %d experts (at most %d are chosen)", top, E, MAX_TOP);
+    LLMB_REQUIRE(E <= 4096, "routed_experts: %d experts (up to 4096 are built)", E);
+    int n_assign = n_tokens * top;
+    int max_tiles = (n_assign + TILE_M - 1) / TILE_M + E;
+    dim3 grid_up((F + BN - 1) / BN, max_tiles), grid_down((hidden + BN - 1) / BN, max_tiles);
+    long long up_stride = 2LL * F * hidden, down_stride = (long long)hidden * F;
+#define LLMB_EXPERTS(T)                                                                                            \
+    do {                                                                                                           \
+        LLMB_CUDA(llmb::launch(router_kernel<T>, dim3(n_tokens), dim3(128), sizeof(float) * E, stream, true,       \
+                               (const T*)h, ld, router, router_bias, hidden, E, top, ids, weights));               \
+        LLMB_CUDA(llmb::launch(plan_kernel, dim3(1), dim3(1024), sizeof(int) * (3 * E + 2), stream, true,          \
+                               (const int*)ids, n_assign, E, sorted, plan, max_tiles));                            \
+    } while (0)
+    if (dtype == LLMB_DTYPE_F32) LLMB_EXPERTS(float);
+    else if (dtype == LLMB_DTYPE_BF16) LLMB_EXPERTS(__nv_bfloat16);
+    else return fail(LLMB_ERR_ARGUMENT, "routed_experts: unknown dtype %d", dtype);
+#undef LLMB_EXPERTS
+    bool tc = tensor_cores && dtype == LLMB_DTYPE_BF16 && hidden % TC_BK == 0 && F % TC_BK == 0 && ld % 8 == 0 &&
+              ((size_t)h % 16) == 0 && ((size_t)w_up % 16) == 0 && ((size_t)w_down % 16) == 0 && ((size_t)act % 16) == 0;
+    if (tc) {
+        typedef __nv_bfloat16 B;
+        LLMB_CUDA(llmb::launch(expert_product_tc_kernel<true>, dim3((F + 63) / 64, max_tiles), dim3(128), 0, stream, true,
+                               (const B*)h, ld, top, (const B*)w_up, up_stride, F, hidden, (const int*)sorted,
+                               (const int*)plan, E, max_tiles, (B*)act, (float*)nullptr, (const float*)nullptr));
+        LLMB_CUDA(llmb::launch(expert_product_tc_kernel<false>, dim3((hidden + 127) / 128, max_tiles), dim3(128), 0, stream,
+                               true, (const B*)act, F, 1, (const B*)w_down, down_stride, hidden, F, (const int*)sorted,
+                               (const int*)plan, E, max_tiles, (B*)nullptr, y, (const float*)weights));
+    } else if (dtype == LLMB_DTYPE_F32) {
+        LLMB_CUDA(llmb::launch(expert_product_kernel<float, true>, grid_up, dim3(256), 0, stream, true, (const float*)h, ld,
+                               top, (const float*)w_up, up_stride, F, hidden, (const int*)sorted, (const int*)plan, E,
+                               max_tiles, (float*)act, (float*)nullptr, (const float*)nullptr));
+        LLMB_CUDA(llmb::launch(expert_product_kernel<float, false>, grid_down, dim3(256), 0, stream, true,
+                               (const float*)act, F, 1, (const float*)w_down, down_stride, hidden, F, (const int*)sorted,
+                               (const int*)plan, E, max_tiles, (float*)nullptr, y, (const float*)weights));
+    } else {
+        typedef __nv_bfloat16 B;
+        LLMB_CUDA(llmb::launch(expert_product_kernel<B, true>, grid_up, dim3(256), 0, stream, true, (const B*)h, ld, top,
+                               (const B*)w_up, up_stride, F, hidden, (const int*)sorted, (const int*)plan, E, max_tiles,
+                               (B*)act, (float*)nullptr, (const float*)nullptr));
+        LLMB_CUDA(llmb::launch(expert_product_kernel<B, false>, grid_down, dim3(256), 0, stream, true, (const B*)act, F, 1,
+                               (const B*)w_down, down_stride, hidden, F, (const int*)sorted, (const int*)plan, E,
+                               max_tiles, (B*)nullptr, y, (const float*)weights));
+    }
+    return check_launch("routed_experts");
+}
+LLMB_PACKED(llmb_routed_experts)

@@ -183,9 +183,17 @@ class DecoderModel:
         def added_before(position):
             return position < len(schedule) and getattr(schedule[position], "add_embedding", False)
 
+        def for_product(e):
+            """What a product's epilogue (or the embedding) can fill: an ops.Emit; anything else a block asks
+            for is left to blocks of its own kind."""
+            return e if isinstance(e, ops.Emit) else None
+
+        def filled(e):
+            return e if e is not None and (e.parts > 0 if isinstance(e, ops.Emit) else getattr(e, "filled", False)) else None
+
         emit = wanted_by(0)
         scale = getattr(self.spec, "embedding_scale", 1.0)
-        x = ops.embed(tokens, self.embedding, scale=scale, emit=emit)
+        x = ops.embed(tokens, self.embedding, scale=scale, emit=for_product(emit))
         # the embedding output, for the runs that add it to the stream again (gathered a second time:
         # every operation of a pass is a launch of this library, so that the pass can be recorded)
         x0 = ops.embed(tokens, self.embedding, scale=scale) if any(added_before(i) for i in range(len(schedule))) else None
@@ -194,11 +202,13 @@ class DecoderModel:
             block = self.blocks[item.layer]
             if added_before(entry):
                 emit = wanted_by(entry)
-                ops.add_rows_(x, x0, emit=emit)
+                ops.add_rows_(x, x0, emit=for_product(emit))
             if getattr(block, "chains_norms", False):
                 # a run before which the embedding is added gets its norm's input from that addition
                 emit_next = None if added_before(entry + 1) else wanted_by(entry + 1)
-                block.forward(x, ctx, entry, cache_entry, normed=emit, emit_next=emit_next)
+                if emit_next is not None and not getattr(block, "accepts_emit", for_product)(emit_next):
+                    emit_next = None
+                block.forward(x, ctx, entry, cache_entry, normed=filled(emit), emit_next=emit_next)
                 emit = emit_next
             else:
                 block.forward(x, ctx, entry, cache_entry)

@@ -415,7 +415,8 @@ def _check_rows(t, n: int, width: int, dtype, what: str):
 
 
 def norm_rope_cache_write(u, q_width, k_width, v_width, q_gain, k_gain, eps, rope_table, rot_unit, interleaved,
-                          tok_pos, tok_seq, q_out, block_table, ring_pages, k_cache, v_cache, write_cache=True):
+                          tok_pos, tok_seq, q_out, block_table, ring_pages, k_cache, v_cache, write_cache=True,
+                          value_source=None):
     """What lies between a projection and the attention of a mixer that norms whole projections:
     the first q_width columns of `u` are the queries, the next k_width the keys, the next v_width
     the values (u may have more columns). With `q_gain` (float32 [q_width]) the queries of a token
@@ -423,10 +424,15 @@ def norm_rope_cache_write(u, q_width, k_width, v_width, q_gain, k_gain, eps, rop
     `k_gain` does the same for the keys. Then every unit of `rot_unit` columns of both is rotated
     by `rope_table` [positions, n_rot] (None: no rotation). Queries go to `q_out` [T, q_width],
     keys into k_cache [pages, Hk, 64, Dk] (Hk * Dk = k_width), values (v_width > 0) into v_cache
-    [pages, Hv, 64, Dv]. Sums, the norm's factor and angles are 32-bit."""
+    [pages, Hv, 64, Dv]. Sums, the norm's factor and angles are 32-bit. `value_source` (a column of u;
+    default q_width + k_width): where a token's values start; q_width makes the values the keys as
+    projected, before norm and rotation (a mixer without a value projection)."""
     _require_cuda(u, q_gain, k_gain, rope_table, tok_pos, tok_seq, q_out, block_table, k_cache, v_cache)
     n = q_out.shape[0]
-    if u.dim() != 2 or u.shape[0] != n or u.shape[1] < q_width + k_width + v_width or u.stride(1) != 1:
+    if value_source is None:
+        value_source = q_width + k_width
+    if (u.dim() != 2 or u.shape[0] != n or u.shape[1] < max(q_width + k_width, value_source + v_width) or u.stride(1) != 1
+            or value_source < 0):
         raise KernelError(f"norm_rope_cache_write: u {tuple(u.shape)} does not hold [{n}, {q_width} + {k_width} + {v_width}]")
     _check_rows(q_out, n, q_width, u.dtype, "norm_rope_cache_write: q_out")
     for gain, width in ((q_gain, q_width), (k_gain, k_width)):
@@ -450,8 +456,163 @@ def norm_rope_cache_write(u, q_width, k_width, v_width, q_gain, k_gain, eps, rop
           _ptr(rope_table), _c_int(n_rot), _c_int(rot_unit), _c_int(1 if interleaved else 0), _ptr(tok_pos),
           _ptr(tok_seq), _ptr(q_out), _c_int(q_out.stride(0)), _ptr(block_table), _c_int(block_table.shape[1]),
           _c_int(ring_pages), _ptr(k_cache), _c_int(k_cache.shape[1]), _ptr(v_cache if v_width else None),
-          _c_int(v_cache.shape[1] if v_width else 0), _c_int(1 if write_cache else 0), _c_int(n), _stream())
+          _c_int(v_cache.shape[1] if v_width else 0), _c_int(1 if write_cache else 0), _c_int(value_source),
+          _c_int(n), _stream())
     return q_out
+
+
+# ----------------------------------------------------------------------------- norms on both sides of a part
+
+def norm_add_(x, y, gain_post, eps_post, terms: int = 1, gain_next=None, eps_next: float = 0.0, out=None,
+              out_dtype=None):
+    """x[t] += s / sqrt(mean(s^2) + eps_post) * gain_post with s = sum_k y[t * terms + k] (y float32
+    [T * terms, hidden]): the norm behind a part and the residual sum. With `gain_next` also
+    out[t] = x[t] / sqrt(mean(x[t]^2) + eps_next) * gain_next in `out_dtype`: the norm in front of the
+    next part, of the updated rows. Returns `out` (or None)."""
+    _require_cuda(x, y, gain_post, gain_next, out)
+    n, hidden = x.shape
+    if (x.dtype != torch.float32 or y.dtype != torch.float32 or not x.is_contiguous() or not y.is_contiguous()
+            or tuple(y.shape) != (n * terms, hidden) or gain_post.dtype != torch.float32 or gain_post.numel() != hidden):
+        raise KernelError(f"norm_add_: x {tuple(x.shape)} and y {tuple(y.shape)} must be contiguous float32 "
+                          f"[T, hidden] and [T * {terms}, hidden], the gain float32 [hidden]")
+    if gain_next is not None:
+        if gain_next.dtype != torch.float32 or gain_next.numel() != hidden:
+            raise KernelError("norm_add_: the next norm's gain must be float32 [hidden]")
+        out_dtype = out_dtype or (out.dtype if out is not None else torch.float32)
+        _check_out(out, (n, hidden), out_dtype, "norm_add_")
+        if out is None:
+            out = torch.empty((n, hidden), dtype=out_dtype, device=x.device)
+    else:
+        out = None
+    _call("post_norm", "llmb_norm_add", _ptr(y), _c_int(terms), _ptr(gain_post), _c_float(eps_post), _ptr(x),
+          _ptr(gain_next), _c_float(eps_next), _ptr(out), _c_int(_code(out.dtype) if out is not None else 0),
+          _c_int(n), _c_int(hidden), _stream())
+    return out
+
+
+def gelu_(a):
+    """a = 0.5 a (1 + tanh(sqrt(2 / pi) (a + 0.044715 a^3))) in place (contiguous; 32-bit arithmetic)."""
+    _require_cuda(a)
+    if not a.is_contiguous():
+        raise KernelError("gelu_: the tensor must be contiguous")
+    _call("post_norm", "llmb_gelu", _ptr(a), _c_int(_code(a.dtype)), ctypes.c_longlong(a.numel()), _stream())
+    return a
+
+
+def sigmoid_gate_(out, gate):
+    """out[t, c] *= sigmoid(gate[t, c]); both [T, width] of one dtype with contiguous rows (either may be a
+    range of columns of a wider buffer)."""
+    _require_cuda(out, gate)
+    n, width = out.shape
+    _check_rows(gate, n, width, out.dtype, "sigmoid_gate_: gate")
+    _check_rows(out, n, width, out.dtype, "sigmoid_gate_: out")
+    _call("post_norm", "llmb_sigmoid_gate", _ptr(out), _c_int(out.stride(0)), _ptr(gate), _c_int(gate.stride(0)),
+          _c_int(_code(out.dtype)), _c_int(n), _c_int(width), _stream())
+    return out
+
+
+def add_terms_(x, y, terms: int):
+    """x[t] += sum_k y[t * terms + k], the terms in index order (both contiguous float32)."""
+    _require_cuda(x, y)
+    n, hidden = x.shape
+    if (x.dtype != torch.float32 or y.dtype != torch.float32 or not x.is_contiguous() or not y.is_contiguous()
+            or y.numel() < n * terms * hidden):
+        raise KernelError("add_terms_: x [T, hidden] and y [T * terms, hidden] must be contiguous float32")
+    _call("post_norm", "llmb_add_terms", _ptr(x), _ptr(y), _c_int(terms), _c_int(n), _c_int(hidden), _stream())
+    return x
+
+
+def fill_(x, value: float):
+    """x[:] = value (float32, contiguous)."""
+    _require_cuda(x)
+    if x.dtype != torch.float32 or not x.is_contiguous():
+        raise KernelError("fill_: the tensor must be contiguous float32")
+    _call("post_norm", "llmb_fill", _ptr(x), ctypes.c_longlong(x.numel()), _c_float(value), _stream())
+    return x
+
+
+# ----------------------------------------------------------------------------- gated delta rule
+
+def delta_rule_work_width(n_heads: int, n_kv_heads: int, dim: int, vdim: int) -> int:
+    """Floats of a token's 32-bit work row: unit q and k, v, beta and decay per head, k.q per key head."""
+    return 2 * n_kv_heads * dim + n_heads * vdim + 2 * n_heads + n_kv_heads
+
+
+def delta_rule(proj, taps, state, tok_seq, cu_seqlens, slot_ids, rate, dt_bias, unit_eps, norm_weight, eps, work, o,
+               mixed, n_heads, n_kv_heads, dim, vdim):
+    """The gated delta rule behind its projection. `proj` [T, >= C + H V + 2 H] (run dtype, rows
+    contiguous) holds per token [q (G D) | k (G D) | v (H V) | gate (H V) | b (H) | a (H)], C = 2 G D + H V.
+    q, k, v pass a causal convolution per channel (`taps` float32 [C, K], the last column the current
+    token's) and silu; q and k become unit vectors per head (q also times D^-1/2); beta = sigmoid(b);
+    decay = exp(rate * softplus(a + dt_bias)) (`rate` float32 [H], negative). Per head, token by token:
+    S <- decay S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q. Then o / sqrt(mean(o^2) + eps) *
+    norm_weight * silu(gate) into `mixed` [T, H V] (run dtype). `state` float32 [slots, (K - 1) C + H D V]:
+    the convolution's last inputs, then S; read and updated for the slots of the step. `work` float32
+    [T, delta_rule_work_width], `o` float32 [T, H V]: scratch."""
+    _require_cuda(proj, taps, state, tok_seq, cu_seqlens, slot_ids, rate, dt_bias, norm_weight, work, o, mixed)
+    n = proj.shape[0]
+    H, G, D, V = n_heads, n_kv_heads, dim, vdim
+    C = 2 * G * D + H * V
+    n_taps = taps.shape[1]
+    if proj.dim() != 2 or proj.shape[1] < C + H * V + 2 * H or proj.stride(1) != 1:
+        raise KernelError(f"delta_rule: the projection {tuple(proj.shape)} does not hold {C + H * V + 2 * H} columns")
+    _check_rows(mixed, n, H * V, proj.dtype, "delta_rule: mixed")
+    for t, shape, what in ((taps, (C, n_taps), "taps"), (rate, (H,), "rate"), (dt_bias, (H,), "dt_bias"),
+                           (norm_weight, (V,), "norm weight"), (o, (n, H * V), "o")):
+        if t.dtype != torch.float32 or tuple(t.shape) != shape or not t.is_contiguous():
+            raise KernelError(f"delta_rule: {what} must be contiguous float32 {shape}")
+    width = delta_rule_work_width(H, G, D, V)
+    if work.dtype != torch.float32 or work.dim() != 2 or work.shape[0] < n or work.shape[1] < width or not work.is_contiguous():
+        raise KernelError(f"delta_rule: work must be contiguous float32 [T, >= {width}]")
+    need = (n_taps - 1) * C + H * D * V
+    if state.dtype != torch.float32 or state.dim() != 2 or state.shape[1] < need or state.stride(1) != 1:
+        raise KernelError(f"delta_rule: the state must be float32 [slots, >= {need}]")
+    _call("delta_rule", "llmb_delta_rule", _ptr(proj), _c_int(proj.stride(0)), _c_int(_code(proj.dtype)), _ptr(taps),
+          _c_int(n_taps), _ptr(state), ctypes.c_longlong(state.stride(0)), _ptr(tok_seq), _ptr(cu_seqlens),
+          _ptr(slot_ids), _ptr(rate), _ptr(dt_bias), _c_float(unit_eps), _ptr(norm_weight), _c_float(eps), _ptr(work),
+          _c_int(work.shape[1]), _ptr(o), _ptr(mixed), _c_int(mixed.stride(0)), _c_int(n), _c_int(cu_seqlens.numel() - 1),
+          _c_int(H), _c_int(G), _c_int(D), _c_int(V), _stream(), kernels=4 if n_taps > 1 else 3)
+    return mixed
+
+
+# ----------------------------------------------------------------------------- routed experts
+
+def routed_experts_plan_ints(n_tokens: int, top: int, n_experts: int) -> int:
+    sizer = load_library("routed_experts").llmb_routed_experts_plan_ints
+    sizer.restype = ctypes.c_longlong
+    return int(sizer(_c_int(n_tokens), _c_int(top), _c_int(n_experts)))
+
+
+def routed_experts(h, router, router_bias, w_up, w_down, top: int, ids, weights, order, plan, act, y):
+    """A feed-forward of routed experts on the rows of h [T, hidden] (run dtype). Router logits
+    z = router h + router_bias in 32-bit (`router` float32 [E, hidden]); the `top` largest are chosen and
+    weighted by the softmax over them. Expert e: W_down,e (silu(W_gate,e h) * (W_up,e h)) with `w_up`
+    [E, 2 F, hidden] (gate rows, then up rows) and `w_down` [E, hidden, F] in h's dtype. Leaves
+    y[t * top + k] = weight[t, k] * expert_(chosen k)(h[t]) as float32 [T * top, hidden]; the caller adds the
+    `top` rows of a token. Scratch: `ids` int32 [T * top], `weights` float32 [T * top], `order` int32 [T * top],
+    `plan` int32 [routed_experts_plan_ints], `act` [T * top, F] in h's dtype."""
+    _require_cuda(h, router, router_bias, w_up, w_down, ids, weights, order, plan, act, y)
+    n, hidden = h.shape
+    E, two_f, _ = w_up.shape
+    F = two_f // 2
+    if (h.stride(1) != 1 or w_up.dtype != h.dtype or w_down.dtype != h.dtype or not w_up.is_contiguous()
+            or not w_down.is_contiguous() or tuple(w_up.shape) != (E, 2 * F, hidden) or tuple(w_down.shape) != (E, hidden, F)):
+        raise KernelError("routed_experts: the expert matrices must be contiguous [E, 2 F, hidden] and [E, hidden, F] in h's dtype")
+    if router.dtype != torch.float32 or tuple(router.shape) != (E, hidden) or not router.is_contiguous():
+        raise KernelError(f"routed_experts: the router must be contiguous float32 [{E}, {hidden}]")
+    if router_bias is not None and (router_bias.dtype != torch.float32 or router_bias.numel() != E):
+        raise KernelError(f"routed_experts: the router's bias must be float32 [{E}]")
+    a = n * top
+    for t, dtype, count, what in ((ids, torch.int32, a, "ids"), (weights, torch.float32, a, "weights"),
+                                  (order, torch.int32, a, "order"), (plan, torch.int32, routed_experts_plan_ints(n, top, E), "plan"),
+                                  (act, h.dtype, a * F, "act"), (y, torch.float32, a * hidden, "y")):
+        if t.dtype != dtype or t.numel() < count or not t.is_contiguous():
+            raise KernelError(f"routed_experts: {what} must be contiguous {dtype} with at least {count} elements")
+    _call("routed_experts", "llmb_routed_experts", _ptr(h), _c_int(h.stride(0)), _c_int(_code(h.dtype)), _ptr(router),
+          _ptr(router_bias), _ptr(w_up), _ptr(w_down), _ptr(ids), _ptr(weights), _ptr(order), _ptr(plan), _ptr(act),
+          _ptr(y), _c_int(n), _c_int(hidden), _c_int(F), _c_int(E), _c_int(top),
+          _c_int(0 if tactics.is_disabled("routed_experts_tc") else 1), _stream(), kernels=4)
+    return y
 
 
 def swiglu(gate_up, out=None):

@@ -4,13 +4,16 @@ from .base import (Block, FeedForward, Mixer, Norm, Part, PositionEncoding, Step
                    register_block, register_feed_forward, register_mixer, register_norm,
                    register_position)
 from .attention import AttentionMixer
-from .block import ParallelBlock, PreNormBlock
+from .block import ParallelBlock, PreNormBlock, SandwichBlock
+from .delta_rule import DeltaRuleMixer
 from .diff_attention import DiffAttentionMixer
-from .feedforward import GatedMlp
+from .feedforward import GatedMlp, Mlp
+from .gated_attention import GatedAttentionMixer
 from .gated_recurrence import GatedRecurrenceMixer
 from .latent_attention import LatentAttentionMixer
 from .norm import RmsNorm, TanhNorm
 from .projected import ProjectedMixer
+from .routed_experts import RoutedExperts
 from .side_by_side import SideBySideMixer
 from .sigmoid_attention import SigmoidAttentionMixer
 from .position import Rope, inverse_frequencies
@@ -20,4 +23,5 @@ __all__ = ["spec", "Block", "FeedForward", "Mixer", "Norm", "Part", "PositionEnc
            "build_position", "register_block", "register_feed_forward", "register_mixer",
            "register_norm", "register_position", "AttentionMixer", "DiffAttentionMixer", "ParallelBlock", "PreNormBlock", "GatedMlp",
            "RmsNorm", "Rope", "inverse_frequencies", "TanhNorm", "ProjectedMixer", "LatentAttentionMixer",
-           "SigmoidAttentionMixer", "GatedRecurrenceMixer", "SideBySideMixer"]
+           "SigmoidAttentionMixer", "GatedRecurrenceMixer", "SideBySideMixer", "SandwichBlock", "DeltaRuleMixer",
+           "GatedAttentionMixer", "Mlp", "RoutedExperts"]

@@ -66,6 +66,12 @@ class Part:
     #: squares); a block runs ops.cast_sumsq behind parts that do not
     emits: bool = False
 
+    #: True if `forward` takes `fresh=True` and then WRITES its result into `residual` (float32
+    #: [T * result_terms, hidden]) instead of adding to it: what a block that norms a part's result needs
+    overwrites: bool = False
+    #: rows of the result a token has when `fresh` (the block adds them in index order)
+    result_terms: int = 1
+
     def parameters(self) -> dict:
         """tensor name -> ParamSpec of everything this part binds."""
         return {}

@@ -315,3 +315,168 @@ class ParallelBlock(Block):
 
 
 register_block("parallel", ParallelBlock)
+
+
+class SandwichBlock(Block):
+    """x += post(mixer(pre(x))); x += post'(feed_forward(pre'(x))): every part stands between two
+    norms, so a part's result is a stream of its own (32-bit, `y`) that is normed before it joins x.
+
+    Launches beside the parts': the first norm of the layer (unless the layer before left it), and
+    behind each part ONE kernel that norms the part's result, adds it to x and norms the new x for the
+    part that runs next (ops.norm_add_): the mixer's post norm with the feed-forward's pre norm, the
+    feed-forward's post norm with the next layer's first norm. A part that can write its result
+    instead of adding it (`Part.overwrites`) gets `fresh=True`; for any other part y is zeroed first.
+    A part may leave several partial results per token (`result_terms`, e.g. one per chosen expert):
+    the kernel adds them in index order."""
+
+    chains_norms = True
+
+    def __init__(self, spec):
+        self.spec = spec
+        self.mixer_norm = build_norm(spec.mixer_norm)
+        self.mixer = build_mixer(spec.mixer)
+        self.mixer_post_norm = build_norm(spec.mixer_post_norm)
+        self.feed_forward = build_feed_forward(spec.feed_forward) if spec.feed_forward is not None else None
+        self.ffn_norm = build_norm(spec.ffn_norm) if self.feed_forward is not None else None
+        self.ffn_post_norm = build_norm(spec.ffn_post_norm) if self.feed_forward is not None else None
+        for norm in (self.mixer_norm, self.mixer_post_norm, self.ffn_norm, self.ffn_post_norm):
+            if norm is not None and not getattr(norm, "foldable", False):
+                raise Unsupported("a sandwich block needs RMS norms (a gain and an eps) on both sides of its parts")
+
+    @property
+    def parts(self):
+        return tuple(p for p in (self.mixer_norm, self.mixer, self.mixer_post_norm, self.ffn_norm, self.feed_forward,
+                                 self.ffn_post_norm) if p is not None)
+
+    @property
+    def graph_safe(self):
+        return all(p.graph_safe for p in self.parts)
+
+    @property
+    def libraries(self):
+        return ("post_norm",) + tuple(lib for p in self.parts for lib in p.libraries)
+
+    def parameters(self):
+        out = {}
+        for p in self.parts:
+            out.update(p.parameters())
+        return out
+
+    def bind(self, tensors, dtype, device):
+        for p in self.parts:
+            p.bind(tensors, dtype, device)
+
+    def replay_key(self, step):
+        keys = [p.replay_key(step) for p in self.parts]
+        return None if any(k is None for k in keys) else tuple(keys)
+
+    def prepare(self, max_positions, device):
+        for p in self.parts:
+            p.prepare(max_positions, device)
+
+    def weights(self):
+        return [w for p in self.parts for w in p.weights()]
+
+    def kernel_shapes(self, dtype, token_counts):
+        return [shape for p in self.parts for shape in p.kernel_shapes(dtype, token_counts)]
+
+    class _Normed:
+        """What the block before leaves for this one: the first norm's output (run dtype), filled."""
+        __slots__ = ("rows", "gain", "eps", "filled")
+
+        def __init__(self, rows, gain, eps):
+            self.rows, self.gain, self.eps, self.filled = rows, gain, eps, False
+
+    @staticmethod
+    def accepts_emit(emit) -> bool:
+        return isinstance(emit, SandwichBlock._Normed)
+
+    def input_emit(self, ctx, n_tokens: int, device):
+        """Where the kernel that last updates x before this block leaves this block's first norm."""
+        rows = ctx.scratch("h_first", (n_tokens, self.spec.mixer_norm.size), ctx.dtype)
+        if rows is None:
+            return None
+        return SandwichBlock._Normed(rows, self.mixer_norm.gain, self.spec.mixer_norm.eps)
+
+    @staticmethod
+    def _terms(part) -> int:
+        return int(getattr(part, "result_terms", 1))
+
+    def scratch_requests(self, n_tokens, dtype):
+        """h_first lives through the whole layer (this layer's last kernel writes the next layer's into
+        it; the mixer has read it by then); y takes the part's result (terms rows a token)."""
+        from ..engine.workspace import BufferRequest
+        hidden = self.spec.mixer_norm.size
+        mixer = self.mixer.scratch_requests(n_tokens, dtype)
+        ffn = self.feed_forward.scratch_requests(n_tokens, dtype) if self.feed_forward is not None else []
+        mixer_end = 1 + max([r.last_use for r in mixer] + [0])
+        ffn_start = mixer_end + 2
+        ffn_end = ffn_start + max([r.last_use for r in ffn] + [0])
+        terms = max(self._terms(self.mixer), self._terms(self.feed_forward) if self.feed_forward is not None else 1)
+        out = [BufferRequest("h_first", (n_tokens, hidden), dtype, 0, ffn_end + 2),
+               BufferRequest("y_part", (n_tokens * terms, hidden), torch.float32, 0, ffn_end + 1)]
+        out += [r.shifted(1, "mixer.") for r in mixer]
+        if self.feed_forward is not None:
+            out.append(BufferRequest("h_ffn", (n_tokens, hidden), dtype, mixer_end + 1, ffn_end))
+            out += [r.shifted(ffn_start, "ffn.") for r in ffn]
+        return out
+
+    def _result(self, ctx, part, n, hidden, device):
+        terms = self._terms(part)
+        y = ctx.scratch("y_part", (n * terms, hidden), torch.float32)
+        if y is None:
+            y = torch.empty((n * terms, hidden), dtype=torch.float32, device=device)
+        fresh = bool(getattr(part, "overwrites", False))
+        if not fresh:
+            ops.fill_(y, 0.0)
+        return y, terms, fresh
+
+    def forward(self, x, ctx, entry, cache_entry, normed=None, emit_next=None):
+        """`normed`: this block's first norm as the block before left it (a filled _Normed), or None.
+        `emit_next`: where this block's last kernel leaves the next block's first norm (a _Normed, or
+        anything else / None: that block norms for itself)."""
+        views = ctx.workspace
+        n, hidden = x.shape
+        s = self.spec
+
+        def prefixed(prefix):
+            if views is not None:
+                views.prefix = prefix
+
+        if isinstance(normed, SandwichBlock._Normed) and normed.filled:
+            h = normed.rows
+        else:
+            h = self.mixer_norm.forward(x, ctx.dtype, out=ctx.scratch("h_first", (n, hidden), ctx.dtype))
+        following = emit_next if isinstance(emit_next, SandwichBlock._Normed) else None
+        y, terms, fresh = self._result(ctx, self.mixer, n, hidden, x.device)
+        prefixed("mixer.")
+        if fresh:
+            self.mixer.forward(h, ctx, entry, cache_entry, y, fresh=True)
+        else:
+            self.mixer.forward(h, ctx, entry, cache_entry, y)
+        prefixed("")
+        if self.feed_forward is None:
+            self._join(x, y, terms, self.mixer_post_norm, following)
+            return
+        h = ops.norm_add_(x, y, self.mixer_post_norm.gain, s.mixer_post_norm.eps, terms, self.ffn_norm.gain,
+                          s.ffn_norm.eps, out=ctx.scratch("h_ffn", (n, hidden), ctx.dtype), out_dtype=ctx.dtype)
+        y, terms, fresh = self._result(ctx, self.feed_forward, n, hidden, x.device)
+        prefixed("ffn.")
+        if fresh:
+            self.feed_forward.forward(h, ctx, y, fresh=True)
+        else:
+            self.feed_forward.forward(h, ctx, y)
+        prefixed("")
+        self._join(x, y, terms, self.ffn_post_norm, following)
+
+    @staticmethod
+    def _join(x, y, terms, post_norm, following):
+        if following is None:
+            ops.norm_add_(x, y, post_norm.gain, post_norm.spec.eps, terms)
+        else:
+            ops.norm_add_(x, y, post_norm.gain, post_norm.spec.eps, terms, following.gain, following.eps,
+                          out=following.rows, out_dtype=following.rows.dtype)
+            following.filled = True
+
+
+register_block("sandwich", SandwichBlock)

@@ -14,6 +14,7 @@ class GatedMlp(FeedForward):
     one matrix product (apps/engine/src/model.rs:1180-1216 of MythEclipse/llm)."""
     graph_safe = True
     emits = True
+    overwrites = True
     libraries = ("elementwise", "gemm_simt", "gemm_skinny", "gemm_tc")
 
     def __init__(self, spec):
@@ -73,7 +74,7 @@ class GatedMlp(FeedForward):
     def replay_key(self, step):
         return ()
 
-    def forward(self, h, ctx, residual, emit=None):
+    def forward(self, h, ctx, residual, emit=None, fresh=False):
         norm = h if isinstance(h, ops.FoldedNorm) else None
         if norm is not None:
             h = norm.rows
@@ -83,7 +84,73 @@ class GatedMlp(FeedForward):
         else:
             gate_up = ops.linear(h, self.w_gate_up, out=ctx.scratch("gate_up", (n, 2 * width), h.dtype), norm=norm)
             act = ops.swiglu(gate_up, out=ctx.scratch("act", (n, width), h.dtype))
-        ops.linear(act, self.w_down, residual=residual, emit=emit)
+        if fresh:
+            ops.linear(act, self.w_down, out_dtype=torch.float32, out=residual)
+        else:
+            ops.linear(act, self.w_down, residual=residual, emit=emit)
 
 
 register_feed_forward("gated_mlp", GatedMlp)
+
+
+class Mlp(FeedForward):
+    """down(act(up h)) with two matrices and the tanh form of gelu,
+    act(z) = 0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3))), added to the residual stream
+    (or, `fresh`, written in its place)."""
+    graph_safe = True
+    emits = True
+    overwrites = True
+    libraries = ("elementwise", "gemm_simt", "gemm_skinny", "gemm_tc", "post_norm")
+
+    def __init__(self, spec):
+        if spec.activation != "gelu_tanh":
+            raise Unsupported(f"activation '{spec.activation}' in a two-matrix feed-forward")
+        self.spec = spec
+        self.w_up = self.w_down = None
+
+    def parameters(self):
+        s, t = self.spec, self.spec.tensor
+        return {t["up"]: ParamSpec((s.intermediate, s.hidden)), t["down"]: ParamSpec((s.hidden, s.intermediate))}
+
+    def bind(self, tensors, dtype, device):
+        t = self.spec.tensor
+        self.w_up = to_run_dtype(tensors[t["up"]], dtype, device)
+        self.w_down = to_run_dtype(tensors[t["down"]], dtype, device)
+
+    def fold_input_norm(self, gain):
+        if self.w_up.dtype != torch.bfloat16 or self.spec.hidden % 8:
+            return False
+        self.w_up = (self.w_up.float() * gain.to(self.w_up.device)[None, :]).to(torch.bfloat16).contiguous()
+        return True
+
+    def kernel_shapes(self, dtype, token_counts):
+        s, out = self.spec, []
+        for n in token_counts:
+            out.append((f"up product, {n} tokens", "linear",
+                        dict(m=n, n=s.intermediate, k=s.hidden, in_dtype=dtype, out_dtype=dtype, lda=s.hidden, aligned=True)))
+            out.append((f"down product, {n} tokens", "linear",
+                        dict(m=n, n=s.hidden, k=s.intermediate, in_dtype=dtype, out_dtype=torch.float32,
+                             lda=s.intermediate, aligned=True)))
+        return out
+
+    def scratch_requests(self, n_tokens, dtype):
+        from ..engine.workspace import BufferRequest
+        # phases: 0 up, 1 activation, 2 down
+        return [BufferRequest("act", (n_tokens, self.spec.intermediate), dtype, 0, 2)]
+
+    def replay_key(self, step):
+        return ()
+
+    def forward(self, h, ctx, residual, emit=None, fresh=False):
+        norm = h if isinstance(h, ops.FoldedNorm) else None
+        if norm is not None:
+            h = norm.rows
+        act = ops.linear(h, self.w_up, out=ctx.scratch("act", (h.shape[0], self.spec.intermediate), h.dtype), norm=norm)
+        ops.gelu_(act)
+        if fresh:
+            ops.linear(act, self.w_down, out_dtype=torch.float32, out=residual)
+        else:
+            ops.linear(act, self.w_down, residual=residual, emit=emit)
+
+
+register_feed_forward("mlp", Mlp)

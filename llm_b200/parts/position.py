@@ -22,6 +22,8 @@ def inverse_frequencies(head_dim: int, theta: float, scaling: dict | None) -> to
     kind = scaling.get("rope_type", scaling.get("type", "default"))
     if kind == "default":
         return freq
+    if kind == "ramp":
+        return _ramp_scaled(freq, head_dim, theta, scaling)
     if kind != "llama3":
         raise Unsupported(f"rope scaling of type '{kind}'")
     factor = float(scaling["factor"])
@@ -32,6 +34,31 @@ def inverse_frequencies(head_dim: int, theta: float, scaling: dict | None) -> to
     blended = (1.0 - smooth) * freq / factor + smooth * freq
     out = torch.where(wavelength > original / low, freq / factor, blended)
     return torch.where(wavelength < original / high, freq, out)
+
+
+def _ramp_scaled(freq, dims: int, theta: float, scaling: dict) -> torch.Tensor:
+    """Frequencies scaled by bands (Peng et al., "YaRN"): with dim(t) = dims ln(original / (2 pi t)) /
+    (2 ln theta) the pair index at which a wave makes t turns over the original context, pairs below
+    lo = floor(dim(fast)) keep their frequency, pairs above hi = ceil(dim(slow)) are slowed by `factor`,
+    and those between are blended linearly in the pair index."""
+    factor, original = float(scaling["factor"]), float(scaling["original"])
+    fast, slow = float(scaling["fast"]), float(scaling["slow"])
+
+    def dim_of(turns):
+        return dims * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(theta))
+
+    lo = max(math.floor(dim_of(fast)), 0)
+    hi = min(math.ceil(dim_of(slow)), dims - 1)
+    pairs = torch.arange(dims // 2, dtype=torch.float64)
+    ramp = torch.clamp((pairs - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+    return freq / factor * ramp + freq * (1.0 - ramp)
+
+
+def table_magnitude(scaling: dict | None) -> float:
+    """What multiplies every cosine and sine of the table: 0.1 ln(factor) + 1 for the 'ramp' scaling, else 1."""
+    if scaling and scaling.get("rope_type", scaling.get("type", "default")) == "ramp":
+        return 0.1 * math.log(float(scaling["factor"])) + 1.0
+    return 1.0
 
 
 class Rope(PositionEncoding):
@@ -56,7 +83,7 @@ class Rope(PositionEncoding):
         if self.table is not None and self.table.shape[0] >= n and self.table.device == torch.device(device):
             return
         angle = torch.arange(n, dtype=torch.float64)[:, None] * self.inv_freq[None, :]
-        table = torch.cat([angle.cos(), angle.sin()], dim=1).to(torch.float32)
+        table = (torch.cat([angle.cos(), angle.sin()], dim=1) * table_magnitude(self.spec.scaling_dict)).to(torch.float32)
         self.table = table.to(device).contiguous()
 
 

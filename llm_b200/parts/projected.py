@@ -20,6 +20,8 @@ class ProjectedMixer(Mixer):
     (or None where a step has no plan)."""
     graph_safe = True
     emits = True
+    #: `forward` takes `fresh=True`: the result is written into `residual` instead of added to it
+    overwrites = True
     w_in = b_in = w_out = None
 
     @property
@@ -83,7 +85,7 @@ class ProjectedMixer(Mixer):
                              lda=self.out_width, aligned=True)))
         return out + self.mix_shapes(dtype, token_counts)
 
-    def forward(self, h, ctx, entry, cache_entry, residual, emit=None):
+    def forward(self, h, ctx, entry, cache_entry, residual, emit=None, fresh=False):
         norm = h if isinstance(h, ops.FoldedNorm) else None
         if norm is not None:
             h = norm.rows
@@ -93,4 +95,7 @@ class ProjectedMixer(Mixer):
         if out is None:
             out = torch.empty((n, self.out_width), dtype=h.dtype, device=h.device)
         self.mix(proj, ctx, entry, cache_entry, out, ctx.scratch)
-        ops.linear(out, self.w_out, residual=residual, emit=emit)
+        if fresh:
+            ops.linear(out, self.w_out, out_dtype=torch.float32, out=residual)
+        else:
+            ops.linear(out, self.w_out, residual=residual, emit=emit)

@@ -1,0 +1,101 @@
+"""A feed-forward of routed experts."""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..errors import FormatError, Unsupported
+from ..weights.loader import ParamSpec
+from .base import FeedForward, register_feed_forward, to_float32, to_run_dtype
+
+
+class RoutedExperts(FeedForward):
+    """Every token goes to the `top` experts with the largest router logits (W_r h + bias, 32-bit;
+    h is the normed input in the run's dtype) and gets their results weighted by the softmax over
+    the chosen logits; an expert is down(silu(gate h) * (up h)).
+
+    One call of ops.routed_experts: the router, a plan made on the device (the tokens of each
+    expert, cut into tiles; nothing comes back to the host, so a step can be captured), one grouped
+    product for gate and up with the activation in its epilogue, one for down with the routing
+    weight. Each (token, chosen expert) leaves a 32-bit row of its own; the sum over a token's
+    rows, in the order of choice, is taken by whoever reads them (`result_terms` rows a token when
+    written fresh; else they are added into the residual here)."""
+    graph_safe = True
+    overwrites = True
+    libraries = ("routed_experts", "post_norm")
+
+    def __init__(self, spec):
+        s = spec
+        if s.activation != "silu":
+            raise Unsupported(f"activation '{s.activation}' in routed experts")
+        if min(s.hidden, s.intermediate, s.n_experts, s.top) < 1 or s.top > s.n_experts:
+            raise FormatError(f"{s.top} of {s.n_experts} experts cannot be chosen")
+        self.spec = spec
+        self.router = self.router_bias = self.w_up = self.w_down = None
+
+    @property
+    def result_terms(self):
+        return self.spec.top
+
+    def parameters(self):
+        s, t = self.spec, self.spec.tensor
+        out = {t["router"]: ParamSpec((s.n_experts, s.hidden))}
+        if s.router_bias:
+            out[t["router_bias"]] = ParamSpec((s.n_experts,), "bias")
+        for e in range(s.n_experts):
+            names = s.expert_tensor(e)
+            out[names["gate"]] = ParamSpec((s.intermediate, s.hidden))
+            out[names["up"]] = ParamSpec((s.intermediate, s.hidden))
+            out[names["down"]] = ParamSpec((s.hidden, s.intermediate))
+        return out
+
+    def bind(self, tensors, dtype, device):
+        s, t = self.spec, self.spec.tensor
+        self.router = to_float32(tensors[t["router"]], device)          # the router is 32-bit in every run
+        self.router_bias = to_float32(tensors[t["router_bias"]], device) if s.router_bias else None
+        ups, downs = [], []
+        for e in range(s.n_experts):
+            names = s.expert_tensor(e)
+            ups.append(torch.cat([to_run_dtype(tensors[names["gate"]], dtype, device),
+                                  to_run_dtype(tensors[names["up"]], dtype, device)]))
+            downs.append(to_run_dtype(tensors[names["down"]], dtype, device))
+        self.w_up = torch.stack(ups).contiguous()                      # [E, 2 F, hidden]
+        self.w_down = torch.stack(downs).contiguous()                  # [E, hidden, F]
+
+    def weights(self):
+        """A decode step reads the router and, per token, `top` experts (counted as if all differed)."""
+        return [self.router]
+
+    def replay_key(self, step):
+        return ()
+
+    def scratch_requests(self, n_tokens, dtype):
+        from ..engine.workspace import BufferRequest
+        s = self.spec
+        a = n_tokens * s.top
+        plan = (s.n_experts + 2 + 3 * ((a + 31) // 32 + s.n_experts),)
+        return [BufferRequest("route_ids", (a,), torch.int32, 0, 0), BufferRequest("route_weights", (a,), torch.float32, 0, 0),
+                BufferRequest("route_order", (a,), torch.int32, 0, 0), BufferRequest("route_plan", plan, torch.int32, 0, 0),
+                BufferRequest("expert_act", (a, s.intermediate), dtype, 0, 0),
+                BufferRequest("expert_rows", (a, s.hidden), torch.float32, 0, 0)]
+
+    def forward(self, h, ctx, residual, fresh=False):
+        s = self.spec
+        n, a = h.shape[0], h.shape[0] * s.top
+        plan_ints = ops.routed_experts_plan_ints(n, s.top, s.n_experts)
+
+        def buffer(name, shape, dtype):
+            t = ctx.scratch(name, shape, dtype)
+            return t if t is not None else torch.empty(shape, dtype=dtype, device=h.device)
+
+        ids, weights = buffer("route_ids", (a,), torch.int32), buffer("route_weights", (a,), torch.float32)
+        order, plan = buffer("route_order", (a,), torch.int32), buffer("route_plan", (plan_ints,), torch.int32)
+        act = buffer("expert_act", (a, s.intermediate), h.dtype)
+        rows = residual if fresh else buffer("expert_rows", (a, s.hidden), torch.float32)
+        ops.routed_experts(h, self.router, self.router_bias, self.w_up, self.w_down, s.top, ids, weights, order, plan,
+                           act, rows)
+        if not fresh:
+            ops.add_terms_(residual, rows, s.top)
+
+
+register_feed_forward("routed_experts", RoutedExperts)

@@ -171,6 +171,55 @@ class GatedRecurrenceSpec:
 
 
 @dataclass(frozen=True)
+class GatedAttentionSpec:
+    """Grouped-query softmax attention whose result is multiplied, element by element, by
+    sigmoid(W_g h) before the output projection (`out_gate`; the gate reads the mixer's input). With
+    `values_are_keys` there is no value projection: a key head's values are its keys as projected,
+    before the rotation (so value_dim == head_dim)."""
+    hidden: int
+    n_heads: int
+    n_kv_heads: int
+    head_dim: int
+    value_dim: int
+    scale: float                     # multiplies q.k
+    window: int                      # 0: every earlier key; w > 0: keys less than w positions back
+    values_are_keys: bool
+    out_gate: bool
+    position: Optional[PositionSpec]
+    names: tuple                     # sorted (role, tensor name): q, k, o (+ v, gate)
+    kind: str = "gated_attention"
+
+    @property
+    def tensor(self):
+        return dict(self.names)
+
+
+@dataclass(frozen=True)
+class DeltaRuleSpec:
+    """The gated delta rule (Yang et al., "Gated Delta Networks"): per head a state matrix S [head_dim,
+    value_dim] with S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q. q, k (n_kv_heads heads,
+    shared by groups of query heads) and v (n_heads heads) pass a causal convolution of `conv_taps` taps
+    per channel and silu; q and k are divided by sqrt(sum of squares + unit_eps), q also by
+    sqrt(head_dim); beta = sigmoid(W_b h); g = exp(-exp(A_log) softplus(W_a h + dt_bias)); every head's o
+    is divided by its root mean square (eps), multiplied by a weight of value_dim elements shared by
+    the heads and by silu(W_g h)."""
+    hidden: int
+    n_heads: int
+    n_kv_heads: int
+    head_dim: int
+    value_dim: int
+    conv_taps: int
+    eps: float                       # of the heads' norm
+    names: tuple                     # sorted (role, tensor name): q, k, v, q_conv, k_conv, v_conv, beta, decay, a_log, dt_bias, gate, norm, o
+    unit_eps: float = 1e-6
+    kind: str = "delta_rule"
+
+    @property
+    def tensor(self):
+        return dict(self.names)
+
+
+@dataclass(frozen=True)
 class SideBySideSpec:
     """Two mixers that read the same input; their results (each times its own `out_scale`) are added."""
     left: object
@@ -189,6 +238,57 @@ class GatedMlpSpec:
     @property
     def tensor(self):
         return dict(self.names)
+
+
+@dataclass(frozen=True)
+class MlpSpec:
+    """down(act(up h)) with two matrices; `activation` 'gelu_tanh' (the tanh form of gelu)."""
+    hidden: int
+    intermediate: int
+    activation: str
+    names: tuple                     # sorted (role, tensor name): up, down
+    kind: str = "mlp"
+
+    @property
+    def tensor(self):
+        return dict(self.names)
+
+
+@dataclass(frozen=True)
+class RoutedExpertsSpec:
+    """A mixture of `n_experts` gated feed-forwards of which a token uses `top`: router logits
+    W_r h (+ bias) in 32-bit, the `top` largest chosen, their weights the softmax over the chosen
+    logits; expert e is down_e(silu(gate_e h) * (up_e h)). `expert_names` holds the (role, name)
+    pairs of one expert with '{e}' in place of its index."""
+    hidden: int
+    intermediate: int
+    n_experts: int
+    top: int
+    router_bias: bool
+    names: tuple                     # sorted (role, tensor name): router (+ router_bias)
+    expert_names: tuple              # sorted (role, pattern): gate, up, down
+    activation: str = "silu"
+    kind: str = "routed_experts"
+
+    @property
+    def tensor(self):
+        return dict(self.names)
+
+    def expert_tensor(self, e: int) -> dict:
+        return {role: pattern.format(e=e) for role, pattern in self.expert_names}
+
+
+@dataclass(frozen=True)
+class SandwichBlockSpec:
+    """x += mixer_post_norm(mixer(mixer_norm(x))); x += ffn_post_norm(feed_forward(ffn_norm(x))): a norm
+    in front of and behind each part. `feed_forward` (with its two norms) may be None."""
+    mixer_norm: object
+    mixer: object
+    mixer_post_norm: object
+    ffn_norm: object
+    feed_forward: object
+    ffn_post_norm: object
+    kind: str = "sandwich"
 
 
 @dataclass(frozen=True)
