@@ -77,6 +77,9 @@ def linear(a, w, bias=None, out_dtype=None, residual=None, out=None, glu=False, 
         if emit is not None:
             cast_sumsq(residual, emit)
         return residual
+    if out is not None:
+        out.copy_(product.to(out.dtype))
+        return out
     return product.to(out_dtype or a.dtype)
 
 
@@ -171,10 +174,12 @@ def tanh_norm(x, alpha, gain, bias, out_dtype, rows=None, out=None, second=None)
 
 
 def norm_rope_cache_write(u, q_width, k_width, v_width, q_gain, k_gain, eps, rope_table, rot_unit, interleaved,
-                          tok_pos, tok_seq, q_out, block_table, ring_pages, k_cache, v_cache, write_cache=True):
+                          tok_pos, tok_seq, q_out, block_table, ring_pages, k_cache, v_cache, write_cache=True,
+                          value_source=None):
     """The first q_width columns of u are the queries, the next k_width the keys, the next v_width
-    the values. With a gain, queries (keys) are divided by the root mean square of the whole
-    segment and multiplied by the gain; then every unit of rot_unit columns of both rotates."""
+    the values (or, with value_source, the v_width columns from there on: q_width makes the values
+    the keys as projected). With a gain, queries (keys) are divided by the root mean square of the
+    whole segment and multiplied by the gain; then every unit of rot_unit columns of both rotates."""
     n = u.shape[0]
     if n == 0:
         return q_out
@@ -196,7 +201,8 @@ def norm_rope_cache_write(u, q_width, k_width, v_width, q_gain, k_gain, eps, rop
         k = segment(q_width, k_width, k_gain)
         k_cache[pages, :, rows, :] = k.reshape(n, k_cache.shape[1], k_cache.shape[3]).to(k_cache.dtype)
         if v_width:
-            v = u[:, q_width + k_width:q_width + k_width + v_width]
+            start = q_width + k_width if value_source is None else value_source
+            v = u[:, start:start + v_width]
             v_cache[pages, :, rows, :] = v.reshape(n, v_cache.shape[1], v_cache.shape[3]).to(v_cache.dtype)
     return q_out
 
@@ -258,6 +264,124 @@ def gated_recurrence(y, x, conv_w, conv_b, gate_a, gate_a_bias, gate_i, gate_i_b
         state[slot, taps - 1] = s
     out.copy_(result.to(out.dtype))
     return out
+
+
+def norm_add_(x, y, gain_post, eps_post, terms=1, gain_next=None, eps_next=0.0, out=None, out_dtype=None):
+    """x[t] += norm(sum of the token's `terms` rows of y); with gain_next also the norm of the new x."""
+    n, hidden = x.shape
+    s = y[:n * terms].view(n, terms, hidden)[:, 0].clone()
+    for k in range(1, terms):                       # the terms in index order
+        s = s + y[:n * terms].view(n, terms, hidden)[:, k]
+    x += s / torch.sqrt((s * s).mean(dim=-1, keepdim=True) + eps_post) * gain_post
+    if gain_next is None:
+        return None
+    normed = (x / torch.sqrt((x * x).mean(dim=-1, keepdim=True) + eps_next) * gain_next)
+    dtype = out_dtype or (out.dtype if out is not None else torch.float32)
+    if out is None:
+        return normed.to(dtype)
+    out.copy_(normed.to(dtype))
+    return out
+
+
+def gelu_(a):
+    z = a.to(torch.float32)
+    a.copy_((0.5 * z * (1.0 + torch.tanh(0.7978845608028654 * (z + 0.044715 * z * z * z)))).to(a.dtype))
+    return a
+
+
+def sigmoid_gate_(out, gate):
+    out.copy_((out.to(torch.float32) * torch.sigmoid(gate.to(torch.float32))).to(out.dtype))
+    return out
+
+
+def add_terms_(x, y, terms):
+    n, hidden = x.shape
+    rows = y.reshape(-1)[:n * terms * hidden].view(n, terms, hidden)
+    for k in range(terms):
+        x += rows[:, k]
+    return x
+
+
+def fill_(x, value):
+    x.fill_(value)
+    return x
+
+
+def delta_rule_work_width(n_heads, n_kv_heads, dim, vdim):
+    return 2 * n_kv_heads * dim + n_heads * vdim + 2 * n_heads + n_kv_heads
+
+
+def delta_rule(proj, taps, state, tok_seq, cu_seqlens, slot_ids, rate, dt_bias, unit_eps, norm_weight, eps, work, o,
+               mixed, n_heads, n_kv_heads, dim, vdim):
+    """Sequence by sequence, token by token, head by head. A token's row of proj is
+    [q (G D) | k (G D) | v (H V) | gate (H V) | b (H) | a (H) | ...]; a slot's row of state is the
+    convolution's last K - 1 inputs [K - 1, C] (oldest first), then S [H, D, V]."""
+    H, G, D, V = n_heads, n_kv_heads, dim, vdim
+    n = proj.shape[0]
+    if n == 0:
+        return mixed
+    C, K = 2 * G * D + H * V, taps.shape[1]
+    cu = cu_seqlens.tolist()
+    result = torch.zeros((n, H * V), dtype=torch.float32, device=proj.device)
+
+    def silu(z):
+        return z / (1.0 + torch.exp(-z))
+
+    for b in range(len(cu) - 1):
+        slot = int(slot_ids[b])
+        history = state[slot, :(K - 1) * C].view(K - 1, C).clone()
+        S = state[slot, (K - 1) * C:(K - 1) * C + H * D * V].view(H, D, V).clone()
+        for t in range(cu[b], cu[b + 1]):
+            row = proj[t].to(torch.float32)
+            rows = torch.cat([history, row[None, :C]])                                    # [K, C]
+            u = silu((taps.T * rows).sum(dim=0))
+            history = rows[1:]
+            q, k, v = u[:G * D].view(G, D), u[G * D:2 * G * D].view(G, D), u[2 * G * D:].view(H, V)
+            q = q / torch.sqrt((q * q).sum(-1, keepdim=True) + unit_eps) / (D ** 0.5)
+            k = k / torch.sqrt((k * k).sum(-1, keepdim=True) + unit_eps)
+            gate = row[C:C + H * V].view(H, V)
+            beta = torch.sigmoid(row[C + H * V:C + H * V + H])
+            z = row[C + H * V + H:C + H * V + 2 * H] + dt_bias
+            decay = torch.exp(rate * torch.where(z > 20.0, z, torch.log1p(torch.exp(torch.clamp(z, max=20.0)))))
+            for a in range(H):
+                g = a // (H // G)
+                S[a] = decay[a] * S[a]
+                w = beta[a] * (v[a] - S[a].T @ k[g])
+                S[a] = S[a] + torch.outer(k[g], w)
+                read = S[a].T @ q[g]
+                read = read / torch.sqrt((read * read).mean() + eps) * norm_weight
+                result[t, a * V:(a + 1) * V] = read * silu(gate[a])
+        state[slot, :(K - 1) * C] = history.reshape(-1)
+        state[slot, (K - 1) * C:(K - 1) * C + H * D * V] = S.reshape(-1)
+    mixed.copy_(result.to(mixed.dtype))
+    return mixed
+
+
+def routed_experts_plan_ints(n_tokens, top, n_experts):
+    return n_experts + 2 + 3 * ((n_tokens * top + 31) // 32 + n_experts)
+
+
+def routed_experts(h, router, router_bias, w_up, w_down, top, ids, weights, order, plan, act, y):
+    """Token by token: 32-bit router logits, the `top` largest, the softmax over them, and one row
+    weight * expert(h) per choice, in the order of choice (largest logit first)."""
+    n, hidden = h.shape
+    F = w_up.shape[1] // 2
+    x = h.to(torch.float32)
+    logits = x @ router.T
+    if router_bias is not None:
+        logits = logits + router_bias
+    for t in range(n):
+        chosen = torch.topk(logits[t], top).indices
+        share = torch.softmax(logits[t, chosen], 0)
+        for k in range(top):
+            e = int(chosen[k])
+            gate_up = x[t] @ w_up[e].to(torch.float32).T
+            g, u = gate_up[:F], gate_up[F:]
+            a = (g / (1.0 + torch.exp(-g)) * u).to(h.dtype).to(torch.float32)
+            y[t * top + k] = share[k] * (a @ w_down[e].to(torch.float32).T)
+            ids[t * top + k] = e
+            weights[t * top + k] = share[k]
+    return y
 
 
 def softcap_(x, cap):
@@ -465,7 +589,9 @@ OPS = {"embed": embed, "scale_": scale_, "cast_sumsq": cast_sumsq, "rmsnorm": rm
        "softcap_": softcap_, "add_rows_": add_rows_, "conv_rope_cache_write": conv_rope_cache_write,
        "diff_attention": diff_attention, "tanh_norm": tanh_norm, "norm_rope_cache_write": norm_rope_cache_write,
        "sigmoid_attention": sigmoid_attention, "gated_recurrence": gated_recurrence,
-       "sample_rows": sample_rows}
+       "sample_rows": sample_rows, "norm_add_": norm_add_, "gelu_": gelu_, "sigmoid_gate_": sigmoid_gate_,
+       "add_terms_": add_terms_, "fill_": fill_, "delta_rule": delta_rule, "delta_rule_work_width": delta_rule_work_width,
+       "routed_experts": routed_experts, "routed_experts_plan_ints": routed_experts_plan_ints}
 
 
 def install(monkeypatch):

@@ -170,9 +170,14 @@ def dense_ff(h, w, p):
     return gelu_tanh(h @ w[p + "up"].T) @ w[p + "down"].T
 
 
-def routed_ff(h, f, w, p):
+def routed_ff(h, f, w, p, margins=None):
+    """`margins` (a list) receives, per token, how far the last chosen logit lies above the first one
+    that is not chosen (infinite where every expert is chosen)."""
     experts, top = int(f["router"]["experts"]), int(f["router"]["top"])
     logits = h @ w[p + "router"].T + w[p + "router.b"]
+    if margins is not None:
+        ranked = torch.sort(logits, dim=-1, descending=True).values
+        margins.append(ranked[:, top - 1] - ranked[:, top] if top < experts else torch.full((h.shape[0],), math.inf, dtype=F))
     out = torch.zeros(h.shape[0], w[p + "e0.down"].shape[0], dtype=F)
     for t in range(h.shape[0]):
         chosen = torch.topk(logits[t], top).indices
@@ -185,9 +190,9 @@ def routed_ff(h, f, w, p):
 
 # ----------------------------------------------------------------------------- the model
 
-def forward(config, w, tokens, layers_out=None):
+def forward(config, w, tokens, layers_out=None, margins=None):
     """Logits [T, vocab] of one sequence from its first token; `layers_out` (a list) receives the
-    stream after every layer."""
+    stream after every layer, `margins` (a list) every routed layer's margins of choice."""
     eps = float(config["norm"]["eps"])
     scale = float(config.get("embedding", {}).get("scale", 1.0)) if config.get("embedding") else 1.0
     x = w["embed"][torch.tensor(tokens, dtype=torch.long)] * scale
@@ -204,8 +209,26 @@ def forward(config, w, tokens, layers_out=None):
         f = layer.get("mlp")
         if f is not None:
             h = rms_norm(x, w[p + "norm2"], eps)
-            y = dense_ff(h, w, p + "mlp.") if f.get("kind", "dense") == "dense" else routed_ff(h, f, w, p + "mlp.")
+            y = dense_ff(h, w, p + "mlp.") if f.get("kind", "dense") == "dense" else routed_ff(h, f, w, p + "mlp.", margins)
             x = x + rms_norm(y, w[p + "norm2b"], eps)
         if layers_out is not None:
             layers_out.append(x.clone())
     return rms_norm(x, w["final.norm"], eps) @ w["embed"].T
+
+
+def greedy(config, w, prompt, n_new):
+    """The n_new tokens that follow the prompt when the largest logit is taken every time."""
+    tokens, out = list(prompt), []
+    for _ in range(n_new):
+        out.append(int(torch.argmax(forward(config, w, tokens)[-1])))
+        tokens.append(out[-1])
+    return out
+
+
+def closest_call(config, w, tokens):
+    """Per token, the smallest margin by which any routed layer chose its experts."""
+    margins = []
+    forward(config, w, tokens, margins=margins)
+    if not margins:
+        return torch.full((len(tokens),), math.inf, dtype=F)
+    return torch.stack(margins).min(dim=0).values
