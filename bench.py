@@ -1,7 +1,7 @@
 """Decode and prefill throughput of the library on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl reference]
-    python bench.py --workload llama-2-7b | llama-3.2-1b | 8b-decode512 | guberax | mefolorn
+    python bench.py --workload llama-2-7b | llama-3.2-1b | 8b-decode512 | guberax | mefolorn | zogapel
 
 The default run has the layer sizes of a Llama-3.1-8B (32 layers, hidden 4096,
 32 heads over 8 kv heads of 128, feed-forward 14336, vocabulary 128256, llama3
@@ -14,7 +14,7 @@ tokens and 128 new tokens each, a Llama-3.2-1B shape with 64 prompts of 1 to 8,1
 256 new tokens at temperature 0.7 (both through `LLM.generate`, host ids in and out), and the
 Llama-3.1-8B shape decoding 256 tokens after prompts of 512 at batch 1, 8 and 64; `guberax`
 times the Guberax architecture beside Llama at equal layer sizes, `mefolorn` the Mefolorn
-architecture beside both. The test names follow the `pp`/`tg`
+architecture beside both, `zogapel` the Zogapel architecture beside Mefolorn and Llama. The test names follow the `pp`/`tg`
 split of MythEclipse/llm's bench (apps/cli/src/bench.rs:10-12): prefill alone,
 and decoding alone on a cache that is already filled.
 """
@@ -338,22 +338,19 @@ def workload_guberax(args):
     return 0
 
 
-def workload_mefolorn(args):
-    """Mefolorn beside Guberax (the library's closest model: parallel blocks, windowed attention, a
-    convolution's state) and Llama at equal layer sizes (the Llama-3.1-8B and Llama-3.2-1B shapes), random
-    bfloat16 weights, `--layers` layers of each (at most 8) plus the head: prefill of 2,048 and 8,192 tokens
-    and decode at batch 8 and 64 over contexts of 2,048 and 8,192, timed with CUDA events, every step on the
-    device. Mefolorn and Guberax run with windows of 2,048; Mefolorn's layers alternate between its two
-    mixers. With LLMB_PROFILE=1 the library prints its per-kernel table for the same steps to standard error."""
+def _beside(args, sizes, metric, headline, sizes_text):
+    """Times the arms of `sizes` ([(size, [(label, config.json contents), ..]), ..]) with random bfloat16 weights:
+    prefill of 2,048 and 8,192 tokens and decode at batch 8 and 64 over contexts of 2,048 and 8,192, timed with CUDA
+    events, every step on the device; prints one line whose `value` is the decode rate of arm `headline` at batch 8
+    and context 8,192. With LLMB_PROFILE=1 the library prints its per-kernel table for the same steps to
+    standard error."""
     import torch
     from llm_b200 import ops
     from llm_b200.config import config_from_dict
     from llm_b200.engine import Engine, Entry, random_model
-    from llm_b200.shapes import shape
 
     torch.cuda.set_device(0)
     device = "cuda:0"
-    layers = min(args.layers, 8)
     peak, peak_source = peaks()
     clocks = ClockSampler()
     clocks.start()
@@ -410,10 +407,7 @@ def workload_mefolorn(args):
 
     steps, warmup = max(16, min(args.steps, 64)), max(args.warmup, 5)
     rows = {}
-    sizes = [("1b", "llama-3.2-1b", "guberax-1b", "mefolorn-1b"), ("8b", "llama-3.1-8b", "guberax-8b", "mefolorn-8b")]
-    for size, llama_name, guberax_name, mefolorn_name in sizes:
-        arms = [("llama", shape(llama_name, layers)), ("guberax_window2048", shape(guberax_name, layers, 2048)),
-                ("mefolorn_window2048", shape(mefolorn_name, layers, 2048))]
+    for size, arms in sizes:
         for label, raw in arms:
             config = config_from_dict(raw)
             vocab = config.model_spec().vocab
@@ -431,19 +425,54 @@ def workload_mefolorn(args):
             torch.cuda.empty_cache()
     clocks.stop()
     print(json.dumps({
-        "metric": "prefill and decode tokens/s, Mefolorn beside Guberax and Llama at equal layer sizes, bf16",
-        "value": rows["mefolorn_window2048-8b"]["decode_b8_c8192"]["tok_s"], "unit": "tokens/s", "n_gpus": 1,
+        "metric": metric, "value": rows[headline]["decode_b8_c8192"]["tok_s"], "unit": "tokens/s", "n_gpus": 1,
         "higher_is_better": True, "dtype": "bf16", "data": "synthetic", "steps": steps, "warmup": warmup,
-        "config": {"layers": layers, "weights": "random N(0,0.02) seed 0", "peaks": peak_source,
-                   "sizes": "8b: width 4096, 32/8 heads of 128, ff 14336, latent 1536 / 128, recurrence 4096 in 16 blocks; "
-                            "1b: width 2048, 32/8 heads of 64, ff 8192, latent 768 / 128, recurrence 2048 in 16 blocks; "
-                            "vocabulary 128256; windows 2048"},
+        "config": {"layers": min(args.layers, 8), "weights": "random N(0,0.02) seed 0", "peaks": peak_source,
+                   "sizes": sizes_text},
         "rows": rows, "gpu_launches": ops.launch_count(), "clocks": clocks.summary()}))
     return 0
 
 
+def workload_mefolorn(args):
+    """Mefolorn beside Guberax (the library's closest model: parallel blocks, windowed attention, a
+    convolution's state) and Llama at equal layer sizes (the Llama-3.1-8B and Llama-3.2-1B shapes), `--layers`
+    layers of each (at most 8) plus the head. Mefolorn and Guberax run with windows of 2,048; Mefolorn's layers
+    alternate between its two mixers."""
+    from llm_b200.shapes import shape
+    layers = min(args.layers, 8)
+    sizes = [(size, [("llama", shape(llama, layers)), ("guberax_window2048", shape(guberax, layers, 2048)),
+                     ("mefolorn_window2048", shape(mefolorn, layers, 2048))])
+             for size, llama, guberax, mefolorn in (("1b", "llama-3.2-1b", "guberax-1b", "mefolorn-1b"),
+                                                    ("8b", "llama-3.1-8b", "guberax-8b", "mefolorn-8b"))]
+    return _beside(args, sizes, "prefill and decode tokens/s, Mefolorn beside Guberax and Llama at equal layer sizes, bf16",
+                   "mefolorn_window2048-8b",
+                   "8b: width 4096, 32/8 heads of 128, ff 14336, latent 1536 / 128, recurrence 4096 in 16 blocks; "
+                   "1b: width 2048, 32/8 heads of 64, ff 8192, latent 768 / 128, recurrence 2048 in 16 blocks; "
+                   "vocabulary 128256; windows 2048")
+
+
+def workload_zogapel(args):
+    """Zogapel beside Mefolorn (the library's closest model: windowed attention beside a recurrence with a
+    convolution's state, a scaled embedding, the embedding as head) and Llama at equal layer sizes (the
+    Llama-3.1-8B and Llama-3.2-1B shapes), `--layers` layers of each (at most 8) plus the head. Both run with
+    windows of 2,048; Zogapel's layers go delta rule, attention, delta rule, attention, the first two with 8 of
+    32 routed experts that together are as wide as the dense feed-forward of the other two."""
+    from llm_b200.shapes import shape
+    layers = min(args.layers, 8)
+    sizes = [(size, [("llama", shape(llama, layers)), ("mefolorn_window2048", shape(mefolorn, layers, 2048)),
+                     ("zogapel_window2048", shape(zogapel, layers, 2048))])
+             for size, llama, mefolorn, zogapel in (("1b", "llama-3.2-1b", "mefolorn-1b", "zogapel-1b"),
+                                                    ("8b", "llama-3.1-8b", "mefolorn-8b", "zogapel-8b"))]
+    return _beside(args, sizes, "prefill and decode tokens/s, Zogapel beside Mefolorn and Llama at equal layer sizes, bf16",
+                   "zogapel_window2048-8b",
+                   "8b: width 4096, 32/8 heads of 128, ff 14336 (dense) or 8 of 32 experts of 1792, delta rule 32/16 heads "
+                   "of 128, 4 taps; 1b: width 2048, 32/8 heads of 64, ff 8192 or 8 of 32 experts of 1024, delta rule "
+                   "32/16 heads of 64; vocabulary 128256; windows 2048")
+
+
 WORKLOADS = {"llama-2-7b": workload_llama_2_7b, "llama-3.2-1b": workload_llama_3_2_1b,
-             "8b-decode512": workload_8b_decode512, "guberax": workload_guberax, "mefolorn": workload_mefolorn}
+             "8b-decode512": workload_8b_decode512, "guberax": workload_guberax, "mefolorn": workload_mefolorn,
+             "zogapel": workload_zogapel}
 
 
 

@@ -12,8 +12,8 @@
 //          unit norms, beta, decay and k.q, into a 32-bit work row [qn | kn | v | beta | decay | kq (G)].
 // conv_state  the convolution's new last inputs; runs behind prepare, which reads the old ones.
 // scan     one block per (columns of S, head, sequence) walks the sequence's tokens in order. Every
-//          column of S is a recurrence of its own: a thread holds 16 elements of one column, DS threads
-//          a column; the two sums over dim use the state before the decay
+//          column of S is a recurrence of its own: a thread holds 16 elements of two columns, DS threads
+//          a pair of columns; the two sums over dim use the state before the decay
 //          (S^T k after the decay is g times the sum before it, and o = g S^T q + u (k.q)), so both
 //          run as independent chains and are added over the DS threads by shuffles. Tokens are
 //          staged in shared memory eight at a time, the next eight requested under the current.
@@ -26,8 +26,7 @@ LLMB_DEFINE_LAST_ERROR(llmb_delta_rule)
 
 constexpr int THREADS = 256;
 constexpr int MAX_TAPS = 16;
-constexpr int DPT = 16;          // elements of a column a thread holds
-constexpr int CHUNK = 8;         // tokens staged at a time
+constexpr int CHUNK = 16;        // tokens staged at a time
 
 __device__ __forceinline__ float silu(float z) { return z / (1.0f + expf(-z)); }
 
@@ -111,53 +110,91 @@ __device__ __forceinline__ void copy4(float* smem, const float* global) {
     unsigned s = (unsigned)__cvta_generic_to_shared(smem);
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(s), "l"(global));
 }
+__device__ __forceinline__ void copy16(float* smem, const float* global) {
+    unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(global));
+}
 
-// DS threads share a column (DS a power of two up to 32); a warp holds 32 / DS columns.
-__global__ void __launch_bounds__(THREADS)
+constexpr int SCAN_THREADS = 128;
+constexpr int NC = 2;            // columns of S a thread holds
+constexpr int PAD = 4;           // floats between the slices of a staged q or k: a quarter warp's 16-byte loads fall into
+                                 // different banks
+
+// DS threads share a pair of columns (DS a power of two up to 32), each DPT elements of both: lanes that follow each
+// other hold neighbouring column pairs of the same slice (their loads of q and k are one address), lanes 32 / DS
+// apart the slices. A step is a chain of dependent instructions (sums, shuffles, the update), so what counts is how
+// many warps a scheduler can turn to: DPT = 8 gives twice the warps of 16 for the same state.
+template <int DPT, int DS>
+__global__ void __launch_bounds__(SCAN_THREADS)
 delta_scan_kernel(const float* __restrict__ work, int work_ld, float* __restrict__ state, long long state_stride,
                   long long s_offset, const int* __restrict__ cu_seqlens, const int* __restrict__ slot_ids,
-                  float* __restrict__ out, int out_ld, int H, int G, int D, int V, int DS) {
-    extern __shared__ float stage[];       // two buffers of [CHUNK] x (q [Dp] | k [Dp] | v [VC] | beta, decay, kq, pad)
+                  float* __restrict__ out, int out_ld, int H, int G, int D, int V, int vectors) {
+    extern __shared__ __align__(16) float stage[];   // two buffers of [CHUNK] x (q [DS][DPT + PAD] | k likewise | v [VC] | beta, decay, kq, -)
     griddep_launch();
     int a = blockIdx.y, b = blockIdx.z;
     int g = a / (H / G);
-    int Dp = DS * DPT, VC = THREADS / DS;
+    constexpr int pairs_per_warp = 32 / DS;
+    constexpr int VC = (SCAN_THREADS / DS) * NC;
     int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    int slice = lane % DS;
-    int col = blockIdx.x * VC + warp * (32 / DS) + lane / DS;
-    int local_col = col - blockIdx.x * VC;
-    int per_token = 2 * Dp + VC + 4, buffer = CHUNK * per_token;
+    int slice = lane / pairs_per_warp;
+    int local_col = (warp * pairs_per_warp + lane % pairs_per_warp) * NC;
+    int col = blockIdx.x * VC + local_col;
+    constexpr int Dq = DS * (DPT + PAD);
+    constexpr int per_token = 2 * Dq + VC + 4, buffer = CHUNK * per_token;
     int GD = G * D, C = 2 * GD + H * V;
     griddep_wait();
     int first = cu_seqlens[b], n = cu_seqlens[b + 1] - first;
     if (n <= 0) return;
     float* S_global = state + (long long)slot_ids[b] * state_stride + s_offset + (size_t)a * D * V;
-    float S[DPT];
+    bool two = (V % 2 == 0) && ((reinterpret_cast<uintptr_t>(S_global) & 7) == 0) && col + 1 < V;
+    float S[NC][DPT];
 #pragma unroll
     for (int e = 0; e < DPT; ++e) {
         int d = slice * DPT + e;
-        S[e] = (d < D && col < V) ? S_global[(size_t)d * V + col] : 0.f;
+        if (two && d < D) {
+            float2 pair = *reinterpret_cast<const float2*>(S_global + (size_t)d * V + col);
+            S[0][e] = pair.x;
+            S[1][e] = pair.y;
+        } else {
+#pragma unroll
+            for (int c = 0; c < NC; ++c) S[c][e] = (d < D && col + c < V) ? S_global[(size_t)d * V + col + c] : 0.f;
+        }
     }
-    // the padding of q and k beyond D stays zero in both buffers
-    for (int i = threadIdx.x; i < 2 * buffer; i += THREADS) stage[i] = 0.f;
+    // the padding of q and k (between slices and beyond D) stays zero in both buffers
+    for (int i = threadIdx.x; i < 2 * buffer; i += SCAN_THREADS) stage[i] = 0.f;
     __syncthreads();
     auto request = [&](int chunk, float* buf) {
         int base = chunk * CHUNK;
         int count = min(CHUNK, n - base);
-        for (int i = threadIdx.x; i < count * per_token; i += THREADS) {
-            int tt = i / per_token, e = i % per_token;
+        for (int tt = warp; tt < count; tt += SCAN_THREADS / 32) {          // a warp a token
             const float* src = work + (size_t)(first + base + tt) * work_ld;
-            float* dst = buf + tt * per_token + e;
-            if (e < Dp) { if (e < D) copy4(dst, src + g * D + e); }
-            else if (e < 2 * Dp) { if (e - Dp < D) copy4(dst, src + GD + g * D + (e - Dp)); }
-            else if (e < 2 * Dp + VC) {
-                int j = blockIdx.x * VC + (e - 2 * Dp);
-                if (j < V) copy4(dst, src + 2 * GD + a * V + j);
+            float* dst = buf + tt * per_token;
+            if (vectors) {
+                // 16 bytes a copy: D, V and the row's length are multiples of 4, so no copy straddles a slice's or D's end
+                int qk = D / 4, vs = min(VC, V - (int)blockIdx.x * VC) / 4;
+                for (int i = lane; i < 2 * qk + vs; i += 32) {
+                    if (i < 2 * qk) {
+                        int which = i >= qk, e = (i - which * qk) * 4;
+                        copy16(dst + which * Dq + (e / DPT) * (DPT + PAD) + e % DPT, src + which * GD + g * D + e);
+                    } else {
+                        int j = (i - 2 * qk) * 4;
+                        copy16(dst + 2 * Dq + j, src + 2 * GD + a * V + blockIdx.x * VC + j);
+                    }
+                }
             } else {
-                int which = e - 2 * Dp - VC;
-                if (which == 0) copy4(dst, src + C + a);
-                else if (which == 1) copy4(dst, src + C + H + a);
-                else if (which == 2) copy4(dst, src + C + 2 * H + g);
+                for (int e = lane; e < 2 * D + VC; e += 32) {
+                    if (e < 2 * D) {
+                        int which = e >= D, d = e - which * D;
+                        copy4(dst + which * Dq + (d / DPT) * (DPT + PAD) + d % DPT, src + which * GD + g * D + d);
+                    } else {
+                        int j = blockIdx.x * VC + (e - 2 * D);
+                        if (j < V) copy4(dst + 2 * Dq + (e - 2 * D), src + 2 * GD + a * V + j);
+                    }
+                }
+            }
+            if (lane < 3) {
+                int at = lane == 0 ? C + a : (lane == 1 ? C + H + a : C + 2 * H + g);
+                copy4(dst + 2 * Dq + VC + lane, src + at);
             }
         }
         asm volatile("cp.async.commit_group;\n" ::);
@@ -176,37 +213,69 @@ delta_scan_kernel(const float* __restrict__ work, int work_ld, float* __restrict
         int count = min(CHUNK, n - chunk * CHUNK);
         for (int tt = 0; tt < count; ++tt) {
             const float* tok = buf + tt * per_token;
-            const float4* q4 = reinterpret_cast<const float4*>(tok + slice * DPT);
-            const float4* k4 = reinterpret_cast<const float4*>(tok + Dp + slice * DPT);
+            const float4* q4 = reinterpret_cast<const float4*>(tok + slice * (DPT + PAD));
+            const float4* k4 = reinterpret_cast<const float4*>(tok + Dq + slice * (DPT + PAD));
             float k[DPT];
-            float sk = 0.f, sq = 0.f;
+            float sk[NC][4] = {}, sq[NC][4] = {};      // four chains a sum: a quarter of the latency of one
 #pragma unroll
             for (int e = 0; e < DPT / 4; ++e) {
                 float4 kv = k4[e], qv = q4[e];
                 k[4 * e] = kv.x; k[4 * e + 1] = kv.y; k[4 * e + 2] = kv.z; k[4 * e + 3] = kv.w;
-                sk = fmaf(S[4 * e], kv.x, sk); sq = fmaf(S[4 * e], qv.x, sq);
-                sk = fmaf(S[4 * e + 1], kv.y, sk); sq = fmaf(S[4 * e + 1], qv.y, sq);
-                sk = fmaf(S[4 * e + 2], kv.z, sk); sq = fmaf(S[4 * e + 2], qv.z, sq);
-                sk = fmaf(S[4 * e + 3], kv.w, sk); sq = fmaf(S[4 * e + 3], qv.w, sq);
-            }
-            for (int offset = DS >> 1; offset > 0; offset >>= 1) {
-                sk += __shfl_xor_sync(0xffffffffu, sk, offset);
-                sq += __shfl_xor_sync(0xffffffffu, sq, offset);
-            }
-            float v = tok[2 * Dp + local_col];
-            float beta = tok[2 * Dp + VC], decay = tok[2 * Dp + VC + 1], kq = tok[2 * Dp + VC + 2];
-            float u = beta * (v - decay * sk);
-            float o = fmaf(u, kq, decay * sq);
 #pragma unroll
-            for (int e = 0; e < DPT; ++e) S[e] = fmaf(k[e], u, decay * S[e]);
-            if (slice == 0 && col < V) out[(size_t)(first + chunk * CHUNK + tt) * out_ld + a * V + col] = o;
+                for (int c = 0; c < NC; ++c) {
+                    sk[c][0] = fmaf(S[c][4 * e], kv.x, sk[c][0]); sq[c][0] = fmaf(S[c][4 * e], qv.x, sq[c][0]);
+                    sk[c][1] = fmaf(S[c][4 * e + 1], kv.y, sk[c][1]); sq[c][1] = fmaf(S[c][4 * e + 1], qv.y, sq[c][1]);
+                    sk[c][2] = fmaf(S[c][4 * e + 2], kv.z, sk[c][2]); sq[c][2] = fmaf(S[c][4 * e + 2], qv.z, sq[c][2]);
+                    sk[c][3] = fmaf(S[c][4 * e + 3], kv.w, sk[c][3]); sq[c][3] = fmaf(S[c][4 * e + 3], qv.w, sq[c][3]);
+                }
+            }
+            float tk[NC], tq[NC];
+#pragma unroll
+            for (int c = 0; c < NC; ++c) {
+                tk[c] = (sk[c][0] + sk[c][1]) + (sk[c][2] + sk[c][3]);
+                tq[c] = (sq[c][0] + sq[c][1]) + (sq[c][2] + sq[c][3]);
+            }
+#pragma unroll
+            for (int offset = 16; offset >= pairs_per_warp; offset >>= 1) {
+#pragma unroll
+                for (int c = 0; c < NC; ++c) {
+                    tk[c] += __shfl_xor_sync(0xffffffffu, tk[c], offset);
+                    tq[c] += __shfl_xor_sync(0xffffffffu, tq[c], offset);
+                }
+            }
+            float2 v = *reinterpret_cast<const float2*>(tok + 2 * Dq + local_col);
+            float beta = tok[2 * Dq + VC], decay = tok[2 * Dq + VC + 1], kq = tok[2 * Dq + VC + 2];
+            float u[NC], o[NC];
+            u[0] = beta * (v.x - decay * tk[0]);
+            u[1] = beta * (v.y - decay * tk[1]);
+#pragma unroll
+            for (int c = 0; c < NC; ++c) {
+                o[c] = fmaf(u[c], kq, decay * tq[c]);
+#pragma unroll
+                for (int e = 0; e < DPT; ++e) S[c][e] = fmaf(k[e], u[c], decay * S[c][e]);
+            }
+            if (slice == 0) {
+                float* dst = out + (size_t)(first + chunk * CHUNK + tt) * out_ld + a * V + col;
+                if (two && (out_ld % 2 == 0) && ((reinterpret_cast<uintptr_t>(out) & 7) == 0)) *reinterpret_cast<float2*>(dst) = make_float2(o[0], o[1]);
+                else {
+#pragma unroll
+                    for (int c = 0; c < NC; ++c)
+                        if (col + c < V) dst[c] = o[c];
+                }
+            }
         }
         __syncthreads();
     }
 #pragma unroll
     for (int e = 0; e < DPT; ++e) {
         int d = slice * DPT + e;
-        if (d < D && col < V) S_global[(size_t)d * V + col] = S[e];
+        if (two && d < D) {
+            *reinterpret_cast<float2*>(S_global + (size_t)d * V + col) = make_float2(S[0][e], S[1][e]);
+        } else {
+#pragma unroll
+            for (int c = 0; c < NC; ++c)
+                if (d < D && col + c < V) S_global[(size_t)d * V + col + c] = S[c][e];
+        }
     }
 }
 
@@ -240,18 +309,32 @@ LLMB_EXPORT int llmb_delta_rule(const void* proj, int ld, int dtype, const float
     if (n_tokens == 0) return LLMB_OK;
     LLMB_REQUIRE(H > 0 && G > 0 && H % G == 0 && D > 0 && V > 0, "delta_rule: bad head sizes %d / %d / %d / %d", H, G, D, V);
     LLMB_REQUIRE(n_taps >= 1 && n_taps <= MAX_TAPS, "delta_rule: %d taps (1 to %d are built)", n_taps, MAX_TAPS);
-    LLMB_REQUIRE(D <= 32 * DPT, "delta_rule: a key size of %d (up to %d is built)", D, 32 * DPT);
+    LLMB_REQUIRE(D <= 32 * 16, "delta_rule: a key size of %d (up to %d is built)", D, 32 * 16);
+    // a long slice per thread (few shuffle levels, long runs of independent products) from a key size of 64 on
+    int DPT = D >= 64 ? 32 : 8;
     int C = 2 * G * D + H * V;
     LLMB_REQUIRE(ld >= C + H * V + 2 * H && work_ld >= C + 2 * H + G, "delta_rule: rows too narrow");
     LLMB_REQUIRE(state_stride >= (long long)(n_taps - 1) * C + (long long)H * D * V, "delta_rule: state too small");
-    LLMB_REQUIRE(work_ld % 1 == 0 && ((size_t)work % 4) == 0, "delta_rule: misaligned work rows");
-    int DS = 1;
+    LLMB_REQUIRE(((size_t)work % 4) == 0, "delta_rule: misaligned work rows");
+    int DS = DPT == 32 ? 2 : 1;
     while (DS * DPT < D) DS *= 2;
-    int VC = THREADS / DS;
+    int VC = (SCAN_THREADS / DS) * NC;
     size_t smem_row = sizeof(float) * (size_t)C;
-    size_t smem_scan = sizeof(float) * 2 * CHUNK * (size_t)(2 * DS * DPT + VC + 4);
+    size_t smem_scan = sizeof(float) * 2 * CHUNK * (size_t)(2 * DS * (DPT + PAD) + VC + 4);
+    // 16-byte copies of a token's q, k and v into the scan's stage: every piece starts on a multiple of 4 floats
+    int vectors = D % 4 == 0 && V % 4 == 0 && work_ld % 4 == 0 && ((size_t)work % 16) == 0 && (V % VC == 0 || V < VC);
     LLMB_REQUIRE(smem_row <= 200 * 1024, "delta_rule: a row of %d channels does not fit in shared memory", C);
     dim3 scan_grid((V + VC - 1) / VC, H, n_seqs);
+    typedef void (*Scan)(const float*, int, float*, long long, long long, const int*, const int*, float*, int, int, int, int, int, int);
+    Scan scan = nullptr;
+    if (DPT == 8) scan = DS == 1 ? delta_scan_kernel<8, 1> : DS == 2 ? delta_scan_kernel<8, 2> : DS == 4 ? delta_scan_kernel<8, 4> : delta_scan_kernel<8, 8>;
+    else scan = DS == 2 ? delta_scan_kernel<32, 2> : DS == 4 ? delta_scan_kernel<32, 4> : DS == 8 ? delta_scan_kernel<32, 8> : delta_scan_kernel<32, 16>;
+    static size_t scan_configured[2][6] = {};
+    int level = DS == 1 ? 0 : DS == 2 ? 1 : DS == 4 ? 2 : DS == 8 ? 3 : DS == 16 ? 4 : 5;
+    if (smem_scan > 48 * 1024 && smem_scan > scan_configured[DPT == 32][level]) {
+        LLMB_CUDA(cudaFuncSetAttribute(scan, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_scan));
+        scan_configured[DPT == 32][level] = smem_scan;
+    }
     long long s_offset = (long long)(n_taps - 1) * C;
 #define LLMB_DELTA(T)                                                                                              \
     do {                                                                                                           \
@@ -264,9 +347,9 @@ LLMB_EXPORT int llmb_delta_rule(const void* proj, int ld, int dtype, const float
         if (n_taps > 1)                                                                                            \
             LLMB_CUDA(llmb::launch(delta_conv_state_kernel<T>, dim3((C + 127) / 128, n_seqs), dim3(128), 0, stream, \
                                    true, (const T*)proj, ld, n_taps, state, state_stride, cu_seqlens, slot_ids, C)); \
-        LLMB_CUDA(llmb::launch(delta_scan_kernel, scan_grid, dim3(THREADS), smem_scan, stream, true,               \
+        LLMB_CUDA(llmb::launch(scan, scan_grid, dim3(SCAN_THREADS), smem_scan, stream, true,                       \
                                (const float*)work, work_ld, state, state_stride, s_offset, cu_seqlens, slot_ids,  \
-                               o, H * V, H, G, D, V, DS));                                                         \
+                               o, H * V, H, G, D, V, vectors));                                                    \
         LLMB_CUDA(llmb::launch(delta_finish_kernel<T>, dim3(n_tokens), dim3(THREADS), 0, stream, true,             \
                                (const float*)o, H * V, (const T*)proj + C, ld, norm_weight, eps, (T*)mixed,        \
                                mixed_ld, H, V));                                                                   \

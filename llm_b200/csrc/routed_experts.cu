@@ -6,7 +6,7 @@
 //          them. An assignment is a pair (token, k): index t * top + k.
 // plan     one block: counts the assignments of every expert, lists them grouped by expert (inside an
 //          expert in rising order, so the plan is a function of the routing alone) and cuts every
-//          expert's list into tiles of TILE_M rows: (expert, first row, rows) per tile. Nothing of this
+//          expert's list into tiles of 32 (or, for the tcgen05 products, 128) rows: (expert, first row, rows) per tile. Nothing of this
 //          reaches the host: the product kernels are launched with the largest possible tile count
 //          and blocks beyond the plan's count leave at once, so a step can be captured and replayed.
 // up       for every tile: act[s, :] = silu(W_gate,e h_t) * (W_up,e h_t) for the rows s of the sorted list
@@ -16,10 +16,17 @@
 // Every output element is one sum over K in rising order, whatever else is in its tile: results do
 // not depend on the batch.
 //
-// Two forms of the products: CUDA cores (any dtype, 32 x 64 tiles) and, for bfloat16 with K % 16 == 0,
-// mma.sync tiles with 32-bit accumulation.
+// Three forms of the products: CUDA cores (any dtype, 32 x 64 tiles); for bfloat16 with K % 32 == 0, mma.sync
+// tiles of 32 rows with 32-bit accumulation (few rows an expert: a decode step streams the weights once); and,
+// for bfloat16 steps with many rows an expert, tcgen05 tiles of 128 rows: the rows of h are gathered in the
+// sorted order once, TMA stages 128 gathered rows and 128 weight rows per k-block of 64 (for the gated product
+// 64 gate rows and the 64 up rows of the same features), one thread issues tcgen05.mma into 128 columns of
+// tensor memory, and four warps read the accumulator back for the activation or the routing weight.
+#include <cuda.h>
+
 #include "common.cuh"
 #include "mma.cuh"
+#include "tc.cuh"
 
 using namespace llmb;
 
@@ -63,7 +70,7 @@ router_kernel(const T* __restrict__ h, int ld, const float* __restrict__ w, cons
 // plan: [0, E] offsets | [E + 1] tile count | then three arrays of max_tiles: expert, first row, rows
 __global__ void __launch_bounds__(1024)
 plan_kernel(const int* __restrict__ ids, int n_assign, int E, int* __restrict__ sorted, int* __restrict__ plan,
-            int max_tiles) {
+            int max_tiles, int tile_m) {
     extern __shared__ int shared[];        // counts [E] | offsets [E + 1] | tile bases [E + 1]
     int* counts = shared;
     int* offsets = shared + E;
@@ -84,7 +91,7 @@ plan_kernel(const int* __restrict__ ids, int n_assign, int E, int* __restrict__ 
             offsets[e] = at;
             bases[e] = tiles;
             at += counts[e];
-            tiles += (counts[e] + TILE_M - 1) / TILE_M;
+            tiles += (counts[e] + tile_m - 1) / tile_m;
         }
         offsets[E] = at;
         bases[E] = tiles;
@@ -97,10 +104,10 @@ plan_kernel(const int* __restrict__ ids, int n_assign, int E, int* __restrict__ 
     int* tile_rows = tile_first + max_tiles;
     for (int e = threadIdx.x; e < E; e += blockDim.x) {
         int n = counts[e];
-        for (int i = 0, tile = bases[e]; i < n && tile < max_tiles; i += TILE_M, ++tile) {
+        for (int i = 0, tile = bases[e]; i < n && tile < max_tiles; i += tile_m, ++tile) {
             tile_expert[tile] = e;
             tile_first[tile] = offsets[e] + i;
-            tile_rows[tile] = min(TILE_M, n - i);
+            tile_rows[tile] = min(tile_m, n - i);
         }
     }
     const unsigned below = (1u << lane) - 1u;
@@ -319,6 +326,214 @@ expert_product_tc_kernel(const __nv_bfloat16* __restrict__ A, int lda, int a_div
     }
 }
 
+// ---------------------------------------------------------------------------------------------- tcgen05
+
+namespace wide {
+
+using namespace llmb::tc;
+
+constexpr int GM = 128, GN = 128, GK = 64, G_THREADS = 192, G_STAGES = 3;
+constexpr int A_BYTES = GM * GK * 2, B_BYTES = GN * GK * 2;
+constexpr size_t G_SMEM = 1024 + (size_t)G_STAGES * (A_BYTES + B_BYTES) + (2 * G_STAGES + 1) * 8 + 16;
+
+// Xs[s, :] = h[sorted[s] / top, :]: the rows of h in the order of the plan (16 bytes a thread a time).
+__global__ void __launch_bounds__(256)
+gather_rows_kernel(const __nv_bfloat16* __restrict__ h, int ld, int top, const int* __restrict__ sorted, int n_assign,
+                   int hidden, __nv_bfloat16* __restrict__ out) {
+    griddep_launch();
+    griddep_wait();
+    int per_row = hidden / 8;
+    long long total = (long long)n_assign * per_row;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        int s = (int)(i / per_row), c = (int)(i % per_row);
+        const uint4* src = reinterpret_cast<const uint4*>(h + (long long)(sorted[s] / top) * ld) + c;
+        reinterpret_cast<uint4*>(out + (long long)s * hidden)[c] = *src;
+    }
+}
+
+// One block: the tile `blockIdx.y` of the plan (an expert's rows [first, first + rows) of the sorted list, at most
+// 128) times the output columns [blockIdx.x * (GLU ? 64 : 128), ..) of that expert. A: [rows of the list, K] behind
+// map_a. B: every expert's matrix stacked, [E * b_rows, K] behind map_b; GLU: an expert's b_rows = 2 N rows are N
+// gate rows, then N up rows, and a stage holds 64 gate rows and the 64 up rows of the same features, so that the
+// accumulator's columns 0..63 are gates and 64..127 the ups. Warp 0: TMA producer. Warp 1: tensor memory and the
+// products. Warps 2..5: epilogue, a thread a row. Every wait is bounded and reports through `status`.
+template <bool GLU>
+__global__ void __launch_bounds__(G_THREADS, 2)
+expert_product_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                           const int* __restrict__ plan, int E, int max_tiles, int b_rows, int N, int n_kblocks,
+                           __nv_bfloat16* __restrict__ act, float* __restrict__ y, const int* __restrict__ sorted,
+                           const float* __restrict__ weights, int* status) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    unsigned char* a_tiles = base;
+    unsigned char* b_tiles = base + (size_t)G_STAGES * A_BYTES;
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(b_tiles + (size_t)G_STAGES * B_BYTES);
+    uint64_t* empty_bar = full_bar + G_STAGES;
+    uint64_t* acc_bar = full_bar + 2 * G_STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_bar + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    griddep_launch();
+    griddep_wait();                                   // the plan is the work of the kernel before
+    int tile = blockIdx.y;
+    if (tile >= plan[E + 1]) return;                  // (before anything is allocated)
+    const int* tile_expert = plan + E + 2;
+    int e = tile_expert[tile], first = tile_expert[max_tiles + tile], rows = tile_expert[2 * max_tiles + tile];
+    int n0 = blockIdx.x * (GLU ? GN / 2 : GN);
+    int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+        for (int s = 0; s < G_STAGES; ++s) {
+            mbar_init(smem_u32(&full_bar[s]), 1);
+            mbar_init(smem_u32(&empty_bar[s]), 1);
+        }
+        mbar_init(smem_u32(acc_bar), 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(tmem_slot)), "r"(GN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int s = 0;
+            uint32_t round = 0;
+            int b_row = e * b_rows + n0;
+            for (int kb = 0; kb < n_kblocks; ++kb) {
+                if (!mbar_wait(smem_u32(&empty_bar[s]), (round & 1) ^ 1, abort_flag, status, 1)) break;
+                uint32_t bar = smem_u32(&full_bar[s]);
+                mbar_expect_tx(bar, A_BYTES + B_BYTES);
+                tma_load_2d(smem_u32(a_tiles + (size_t)s * A_BYTES), &map_a, bar, kb * GK, first);
+                if (GLU) {
+                    tma_load_2d(smem_u32(b_tiles + (size_t)s * B_BYTES), &map_b, bar, kb * GK, b_row);
+                    tma_load_2d(smem_u32(b_tiles + (size_t)s * B_BYTES + B_BYTES / 2), &map_b, bar, kb * GK, b_row + N);
+                } else {
+                    tma_load_2d(smem_u32(b_tiles + (size_t)s * B_BYTES), &map_b, bar, kb * GK, b_row);
+                }
+                if (++s == G_STAGES) { s = 0; ++round; }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // instruction descriptor: D 32-bit, A and B bfloat16, both K-major, N = 128, M = 128
+            constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(GN >> 3) << 17) | ((uint32_t)(GM >> 4) << 24);
+            const uint64_t a_desc0 = smem_desc(smem_u32(a_tiles)), b_desc0 = smem_desc(smem_u32(b_tiles));
+            int s = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int kb = 0; kb < n_kblocks; ++kb) {
+                ok = mbar_wait(smem_u32(&full_bar[s]), phase, abort_flag, status, 2);
+                if (!ok) break;
+                tcgen05_fence_after();
+                uint64_t a_desc = a_desc0 + (uint64_t)(s * (A_BYTES >> 4));
+                uint64_t b_desc = b_desc0 + (uint64_t)(s * (B_BYTES >> 4));
+#pragma unroll
+                for (int k = 0; k < GK / 16; ++k)               // 16 k-values = 32 bytes inside the swizzled row
+                    tcgen05_mma(tmem_base, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                tcgen05_commit(smem_u32(&empty_bar[s]));
+                if (++s == G_STAGES) { s = 0; phase ^= 1; }
+            }
+            if (ok) tcgen05_commit(smem_u32(acc_bar));
+        }
+    } else {
+        int quarter = warp & 3;                                  // the 32 lanes of tensor memory this warp may read
+        int row = quarter * 32 + lane;
+        bool ok = mbar_wait(smem_u32(acc_bar), 0, abort_flag, status, 3);
+        ok = __all_sync(0xffffffffu, ok);
+        if (ok) {
+            tcgen05_fence_after();
+            uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+            bool live = row < rows;
+            if (GLU) {
+                __nv_bfloat16* out = act + (long long)(first + row) * N + n0;
+                bool vector = N % 8 == 0;
+#pragma unroll 1
+                for (int c = 0; c < GN / 2; c += 16) {
+                    uint32_t g[16], u[16];
+                    tmem_ld16(taddr + c, g);
+                    tmem_ld16(taddr + GN / 2 + c, u);
+                    if (!live || n0 + c >= N) continue;
+                    float v[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        float gate = __uint_as_float(g[j]);
+                        v[j] = gate / (1.0f + expf(-gate)) * __uint_as_float(u[j]);
+                    }
+                    if (vector && n0 + c + 16 <= N) {
+                        uint32_t packed[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            __nv_bfloat162 two = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+                            packed[j] = *reinterpret_cast<uint32_t*>(&two);
+                        }
+                        uint4* dst = reinterpret_cast<uint4*>(out + c);
+                        dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                        dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (n0 + c + j < N) out[c + j] = __float2bfloat16_rn(v[j]);
+                    }
+                }
+            } else {
+                int assignment = live ? sorted[first + row] : 0;
+                float wgt = live ? weights[assignment] : 0.f;
+                float* out = y + (long long)assignment * N + n0;
+                bool vector = N % 4 == 0;
+#pragma unroll 1
+                for (int c = 0; c < GN; c += 16) {
+                    uint32_t r[16];
+                    tmem_ld16(taddr + c, r);
+                    if (!live || n0 + c >= N) continue;
+                    if (vector && n0 + c + 16 <= N) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            reinterpret_cast<float4*>(out + c)[j] =
+                                make_float4(wgt * __uint_as_float(r[4 * j]), wgt * __uint_as_float(r[4 * j + 1]),
+                                            wgt * __uint_as_float(r[4 * j + 2]), wgt * __uint_as_float(r[4 * j + 3]));
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (n0 + c + j < N) out[c + j] = wgt * __uint_as_float(r[j]);
+                    }
+                }
+            }
+        }
+    }
+
+    // teardown: everyone meets, then the allocating warp frees the tensor memory
+    tcgen05_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        for (int i = 0; i < 100; ++i) __nanosleep(10000);          // copies in flight land before shared memory is given up
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tcgen05_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(GN) : "memory");
+    }
+}
+
+}  // namespace wide
+
+LLMB_EXPORT int llmb_routed_experts_status() {
+    int* s = llmb::tc::status_word();
+    if (!s) return -1;
+    int v = *s;
+    *s = 0;
+    return v;
+}
+
 LLMB_EXPORT long long llmb_routed_experts_plan_ints(int n_tokens, int top, int E) {
     long long max_tiles = ((long long)n_tokens * top + TILE_M - 1) / TILE_M + E;
     return (long long)E + 2 + 3 * max_tiles;
@@ -326,11 +541,13 @@ LLMB_EXPORT long long llmb_routed_experts_plan_ints(int n_tokens, int top, int E
 
 // h [T, ld] in `dtype`; router float32 [E, hidden] and bias float32 [E] (or null); w_up [E, 2 F, hidden] (gate rows,
 // then up rows) and w_down [E, hidden, F] in `dtype`; ids int32 [T * top], weights float32 [T * top], sorted
-// int32 [T * top], plan int32 [plan_ints]; act [T * top, F] in `dtype`; y float32 [T * top, hidden].
+// int32 [T * top], plan int32 [plan_ints]; act [T * top, F] in `dtype`; y float32 [T * top, hidden]. `tensor_cores`:
+// 0 CUDA cores only, 1 also the mma.sync tiles, 2 also the tcgen05 tiles of 128 rows, which need `gathered`
+// (bfloat16 [T * top, hidden] scratch) and are taken when the step has that scratch.
 LLMB_EXPORT int llmb_routed_experts(const void* h, int ld, int dtype, const float* router, const float* router_bias,
                                     const void* w_up, const void* w_down, int* ids, float* weights, int* sorted,
-                                    int* plan, void* act, float* y, int n_tokens, int hidden, int F, int E, int top,
-                                    int tensor_cores, cudaStream_t stream) {
+                                    int* plan, void* act, float* y, void* gathered, int n_tokens, int hidden, int F,
+                                    int E, int top, int tensor_cores, cudaStream_t stream) {
     if (n_tokens == 0) return LLMB_OK;
     LLMB_REQUIRE(hidden > 0 && F > 0 && E > 0 && top > 0 && top <= E && top <= MAX_TOP,
                  "routed_experts: %d of %d experts (at most %d are chosen)", top, E, MAX_TOP);
@@ -339,20 +556,55 @@ LLMB_EXPORT int llmb_routed_experts(const void* h, int ld, int dtype, const floa
     int max_tiles = (n_assign + TILE_M - 1) / TILE_M + E;
     dim3 grid_up((F + BN - 1) / BN, max_tiles), grid_down((hidden + BN - 1) / BN, max_tiles);
     long long up_stride = 2LL * F * hidden, down_stride = (long long)hidden * F;
+    bool aligned = ld % 8 == 0 && ((size_t)h % 16) == 0 && ((size_t)w_up % 16) == 0 && ((size_t)w_down % 16) == 0 &&
+                   ((size_t)act % 16) == 0;
+    bool wide_tiles = tensor_cores >= 2 && dtype == LLMB_DTYPE_BF16 && gathered && hidden % 8 == 0 && F % 8 == 0 && aligned &&
+                      ((size_t)gathered % 16) == 0 && ((size_t)y % 16) == 0 && (long long)E * 2 * F < (1LL << 31) &&
+                      (long long)E * hidden < (1LL << 31);
+    int tile_m = wide_tiles ? wide::GM : TILE_M;
 #define LLMB_EXPERTS(T)                                                                                            \
     do {                                                                                                           \
         LLMB_CUDA(llmb::launch(router_kernel<T>, dim3(n_tokens), dim3(128), sizeof(float) * E, stream, true,       \
                                (const T*)h, ld, router, router_bias, hidden, E, top, ids, weights));               \
         LLMB_CUDA(llmb::launch(plan_kernel, dim3(1), dim3(1024), sizeof(int) * (3 * E + 2), stream, true,          \
-                               (const int*)ids, n_assign, E, sorted, plan, max_tiles));                            \
+                               (const int*)ids, n_assign, E, sorted, plan, max_tiles, tile_m));                    \
     } while (0)
     if (dtype == LLMB_DTYPE_F32) LLMB_EXPERTS(float);
     else if (dtype == LLMB_DTYPE_BF16) LLMB_EXPERTS(__nv_bfloat16);
     else return fail(LLMB_ERR_ARGUMENT, "routed_experts: unknown dtype %d", dtype);
 #undef LLMB_EXPERTS
-    bool tc = tensor_cores && dtype == LLMB_DTYPE_BF16 && hidden % TC_BK == 0 && F % TC_BK == 0 && ld % 8 == 0 &&
-              ((size_t)h % 16) == 0 && ((size_t)w_up % 16) == 0 && ((size_t)w_down % 16) == 0 && ((size_t)act % 16) == 0;
-    if (tc) {
+    bool tc = tensor_cores && dtype == LLMB_DTYPE_BF16 && hidden % TC_BK == 0 && F % TC_BK == 0 && aligned;
+    if (wide_tiles) {
+        typedef __nv_bfloat16 B;
+        using namespace wide;
+        static bool configured = false;
+        if (!configured) {
+            LLMB_CUDA(cudaFuncSetAttribute(expert_product_wide_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)G_SMEM));
+            LLMB_CUDA(cudaFuncSetAttribute(expert_product_wide_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)G_SMEM));
+            configured = true;
+        }
+        int* status_dev = nullptr;
+        int* status_host = llmb::tc::status_word();
+        if (status_host) LLMB_CUDA(cudaHostGetDevicePointer((void**)&status_dev, status_host, 0));
+        CUtensorMap map_x, map_up, map_act, map_down;
+        int code = llmb::tc::make_map_2d(&map_x, gathered, n_assign, hidden, hidden, GK, GM);
+        if (!code) code = llmb::tc::make_map_2d(&map_up, w_up, (long long)E * 2 * F, hidden, hidden, GK, GN / 2);
+        if (!code) code = llmb::tc::make_map_2d(&map_act, act, n_assign, F, F, GK, GM);
+        if (!code) code = llmb::tc::make_map_2d(&map_down, w_down, (long long)E * hidden, F, F, GK, GN);
+        if (code) return code;
+        int tiles = (n_assign + GM - 1) / GM + E;
+        if (tiles > max_tiles) tiles = max_tiles;
+        long long vectors = (long long)n_assign * (hidden / 8);
+        int gather_blocks = (int)((vectors + 255) / 256 < 148 * 8 ? (vectors + 255) / 256 : 148 * 8);
+        LLMB_CUDA(llmb::launch(gather_rows_kernel, dim3(gather_blocks), dim3(256), 0, stream, true, (const B*)h, ld, top,
+                               (const int*)sorted, n_assign, hidden, (B*)gathered));
+        LLMB_CUDA(llmb::launch(expert_product_wide_kernel<true>, dim3((F + GN / 2 - 1) / (GN / 2), tiles), dim3(G_THREADS), G_SMEM,
+                               stream, true, map_x, map_up, (const int*)plan, E, max_tiles, 2 * F, F, (hidden + GK - 1) / GK,
+                               (B*)act, (float*)nullptr, (const int*)sorted, (const float*)nullptr, status_dev));
+        LLMB_CUDA(llmb::launch(expert_product_wide_kernel<false>, dim3((hidden + GN - 1) / GN, tiles), dim3(G_THREADS), G_SMEM,
+                               stream, true, map_act, map_down, (const int*)plan, E, max_tiles, hidden, hidden,
+                               (F + GK - 1) / GK, (B*)nullptr, y, (const int*)sorted, (const float*)weights, status_dev));
+    } else if (tc) {
         typedef __nv_bfloat16 B;
         LLMB_CUDA(llmb::launch(expert_product_tc_kernel<true>, dim3((F + 63) / 64, max_tiles), dim3(128), 0, stream, true,
                                (const B*)h, ld, top, (const B*)w_up, up_stride, F, hidden, (const int*)sorted,

@@ -534,8 +534,9 @@ def fill_(x, value: float):
 # ----------------------------------------------------------------------------- gated delta rule
 
 def delta_rule_work_width(n_heads: int, n_kv_heads: int, dim: int, vdim: int) -> int:
-    """Floats of a token's 32-bit work row: unit q and k, v, beta and decay per head, k.q per key head."""
-    return 2 * n_kv_heads * dim + n_heads * vdim + 2 * n_heads + n_kv_heads
+    """Floats of a token's 32-bit work row: unit q and k, v, beta and decay per head, k.q per key head; rounded up to
+    16 bytes so that a row starts where a 16-byte copy may start."""
+    return (2 * n_kv_heads * dim + n_heads * vdim + 2 * n_heads + n_kv_heads + 3) // 4 * 4
 
 
 def delta_rule(proj, taps, state, tok_seq, cu_seqlens, slot_ids, rate, dt_bias, unit_eps, norm_weight, eps, work, o,
@@ -583,15 +584,29 @@ def routed_experts_plan_ints(n_tokens: int, top: int, n_experts: int) -> int:
     return int(sizer(_c_int(n_tokens), _c_int(top), _c_int(n_experts)))
 
 
-def routed_experts(h, router, router_bias, w_up, w_down, top: int, ids, weights, order, plan, act, y):
+#: the tcgen05 tiles of 128 rows are taken from this many rows an expert (on average) on; below, a step streams the
+#: experts' matrices once whatever the tile, and the 32-row tiles waste less of a block
+WIDE_EXPERT_ROWS = 32
+
+
+def routed_experts_wide(n_tokens: int, top: int, n_experts: int, hidden: int, intermediate: int, dtype) -> bool:
+    """True if a step of n_tokens takes the tcgen05 form of the experts' products (and so needs the scratch for
+    the gathered rows)."""
+    return (dtype == torch.bfloat16 and hidden % 8 == 0 and intermediate % 8 == 0
+            and n_tokens * top >= WIDE_EXPERT_ROWS * n_experts and not tactics.is_disabled("routed_experts_tc")
+            and not tactics.is_disabled("routed_experts_wide"))
+
+
+def routed_experts(h, router, router_bias, w_up, w_down, top: int, ids, weights, order, plan, act, y, gathered=None):
     """A feed-forward of routed experts on the rows of h [T, hidden] (run dtype). Router logits
     z = router h + router_bias in 32-bit (`router` float32 [E, hidden]); the `top` largest are chosen and
     weighted by the softmax over them. Expert e: W_down,e (silu(W_gate,e h) * (W_up,e h)) with `w_up`
     [E, 2 F, hidden] (gate rows, then up rows) and `w_down` [E, hidden, F] in h's dtype. Leaves
     y[t * top + k] = weight[t, k] * expert_(chosen k)(h[t]) as float32 [T * top, hidden]; the caller adds the
     `top` rows of a token. Scratch: `ids` int32 [T * top], `weights` float32 [T * top], `order` int32 [T * top],
-    `plan` int32 [routed_experts_plan_ints], `act` [T * top, F] in h's dtype."""
-    _require_cuda(h, router, router_bias, w_up, w_down, ids, weights, order, plan, act, y)
+    `plan` int32 [routed_experts_plan_ints], `act` [T * top, F] in h's dtype, and, for the steps that
+    routed_experts_wide names, `gathered` [T * top, hidden] in h's dtype (the rows of h in the plan's order)."""
+    _require_cuda(h, router, router_bias, w_up, w_down, ids, weights, order, plan, act, y, gathered)
     n, hidden = h.shape
     E, two_f, _ = w_up.shape
     F = two_f // 2
@@ -608,10 +623,14 @@ def routed_experts(h, router, router_bias, w_up, w_down, top: int, ids, weights,
                                   (act, h.dtype, a * F, "act"), (y, torch.float32, a * hidden, "y")):
         if t.dtype != dtype or t.numel() < count or not t.is_contiguous():
             raise KernelError(f"routed_experts: {what} must be contiguous {dtype} with at least {count} elements")
+    wide = gathered is not None and routed_experts_wide(n, top, E, hidden, F, h.dtype)
+    if wide and (gathered.dtype != h.dtype or gathered.numel() < a * hidden or not gathered.is_contiguous()):
+        raise KernelError(f"routed_experts: gathered must be contiguous {h.dtype} with at least {a * hidden} elements")
+    level = 0 if tactics.is_disabled("routed_experts_tc") else (2 if wide else 1)
     _call("routed_experts", "llmb_routed_experts", _ptr(h), _c_int(h.stride(0)), _c_int(_code(h.dtype)), _ptr(router),
           _ptr(router_bias), _ptr(w_up), _ptr(w_down), _ptr(ids), _ptr(weights), _ptr(order), _ptr(plan), _ptr(act),
-          _ptr(y), _c_int(n), _c_int(hidden), _c_int(F), _c_int(E), _c_int(top),
-          _c_int(0 if tactics.is_disabled("routed_experts_tc") else 1), _stream(), kernels=4)
+          _ptr(y), _ptr(gathered if wide else None), _c_int(n), _c_int(hidden), _c_int(F), _c_int(E), _c_int(top),
+          _c_int(level), _stream(), kernels=5 if wide else 4)
     return y
 
 
@@ -759,7 +778,7 @@ def check_device_status() -> None:
     """Raise if a kernel of a loaded library reported a wait that ran out. Cheap (it
     reads a word of host memory); meaningful after the stream was synchronised."""
     from .build import _loaded
-    for name in ("gemm_tc", "attention_prefill_tc"):
+    for name in ("gemm_tc", "attention_prefill_tc", "routed_experts"):
         if name in _loaded:
             code = getattr(_loaded[name], f"llmb_{name}_status")()
             if code != 0:

@@ -17,9 +17,10 @@ class RoutedExperts(FeedForward):
     One call of ops.routed_experts: the router, a plan made on the device (the tokens of each
     expert, cut into tiles; nothing comes back to the host, so a step can be captured), one grouped
     product for gate and up with the activation in its epilogue, one for down with the routing
-    weight. Each (token, chosen expert) leaves a 32-bit row of its own; the sum over a token's
-    rows, in the order of choice, is taken by whoever reads them (`result_terms` rows a token when
-    written fresh; else they are added into the residual here)."""
+    weight (tcgen05 tiles of 128 rows where a step brings many rows an expert, tiles of 32 else).
+    Each (token, chosen expert) leaves a 32-bit row of its own; the sum over a token's rows, in the
+    order of choice, is taken by whoever reads them (`result_terms` rows a token when written
+    fresh; else they are added into the residual here)."""
     graph_safe = True
     overwrites = True
     libraries = ("routed_experts", "post_norm")
@@ -74,10 +75,13 @@ class RoutedExperts(FeedForward):
         s = self.spec
         a = n_tokens * s.top
         plan = (s.n_experts + 2 + 3 * ((a + 31) // 32 + s.n_experts),)
-        return [BufferRequest("route_ids", (a,), torch.int32, 0, 0), BufferRequest("route_weights", (a,), torch.float32, 0, 0),
-                BufferRequest("route_order", (a,), torch.int32, 0, 0), BufferRequest("route_plan", plan, torch.int32, 0, 0),
-                BufferRequest("expert_act", (a, s.intermediate), dtype, 0, 0),
-                BufferRequest("expert_rows", (a, s.hidden), torch.float32, 0, 0)]
+        out = [BufferRequest("route_ids", (a,), torch.int32, 0, 0), BufferRequest("route_weights", (a,), torch.float32, 0, 0),
+               BufferRequest("route_order", (a,), torch.int32, 0, 0), BufferRequest("route_plan", plan, torch.int32, 0, 0),
+               BufferRequest("expert_act", (a, s.intermediate), dtype, 0, 0),
+               BufferRequest("expert_rows", (a, s.hidden), torch.float32, 0, 0)]
+        if ops.routed_experts_wide(n_tokens, s.top, s.n_experts, s.hidden, s.intermediate, dtype):
+            out.append(BufferRequest("expert_in", (a, s.hidden), dtype, 0, 0))       # the rows of h in the plan's order
+        return out
 
     def forward(self, h, ctx, residual, fresh=False):
         s = self.spec
@@ -92,8 +96,10 @@ class RoutedExperts(FeedForward):
         order, plan = buffer("route_order", (a,), torch.int32), buffer("route_plan", (plan_ints,), torch.int32)
         act = buffer("expert_act", (a, s.intermediate), h.dtype)
         rows = residual if fresh else buffer("expert_rows", (a, s.hidden), torch.float32)
+        wide = ops.routed_experts_wide(n, s.top, s.n_experts, s.hidden, s.intermediate, h.dtype)
+        gathered = buffer("expert_in", (a, s.hidden), h.dtype) if wide else None
         ops.routed_experts(h, self.router, self.router_bias, self.w_up, self.w_down, s.top, ids, weights, order, plan,
-                           act, rows)
+                           act, rows, gathered)
         if not fresh:
             ops.add_terms_(residual, rows, s.top)
 

@@ -69,6 +69,29 @@ SHAPES["mefolorn-8b"] = _mefolorn(4096, 32, 8, 128, 14336, 128256, 32, 2048, 153
 SHAPES["mefolorn-1b"] = _mefolorn(2048, 32, 8, 64, 8192, 128256, 16, 2048, 768, 128, 16)
 
 
+def _zogapel(width, heads, kv_heads, dim, ff, vocab, layers, window, experts, top):
+    """A Zogapel configuration whose layers match a Llama shape in size (width, heads, head size, feed-forward,
+    vocabulary): a pattern of four layers, delta rule and windowed attention in turn (the delta rule with the
+    Llama shape's heads over half as many key heads, values as wide as keys, four taps; the attention rotating
+    half of each head, frequencies scaled by bands), the first two with routed experts whose `top` chosen ones
+    together are as wide as the dense feed-forward of the other two."""
+    delta = {"heads": heads, "kv_heads": max(1, heads // 2), "dim": dim, "vdim": dim, "conv": 4}
+    attention = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "mask": {"size": window},
+                 "rot": {"base": 500000.0, "dims": dim // 2,
+                         "scaling": {"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0}}}
+    dense = {"kind": "dense", "ff": ff}
+    routed = {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": ff // top}}
+    kinds = [{"type": "delta", "mixer": delta, "mlp": routed}, {"type": "attention", "mixer": attention, "mlp": routed},
+             {"type": "delta", "mixer": delta, "mlp": dense}, {"type": "attention", "mixer": attention, "mlp": dense}]
+    return {"architecture": "Zogapel", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},
+            "layers": [kinds[i % 4] for i in range(layers)]}
+
+
+# the layer sizes of llama-3.1-8b and llama-3.2-1b; windows of 2,048 unless a run sets another; 8 of 32 experts
+SHAPES["zogapel-8b"] = _zogapel(4096, 32, 8, 128, 14336, 128256, 32, 2048, 32, 8)
+SHAPES["zogapel-1b"] = _zogapel(2048, 32, 8, 64, 8192, 128256, 16, 2048, 32, 8)
+
+
 def shape(name: str, layers: int | None = None, window: int | None = None) -> dict:
     """A copy of the named shape's config.json, optionally with fewer layers (and, for a shape
     with windowed attention, another window)."""

@@ -5,6 +5,10 @@
     python microbench.py attention_prefill --tokens 2048
     python microbench.py rmsnorm --m 8 --k 4096
     python microbench.py sample --batch 8 --n 128256 [--temperature 0.7]
+    python microbench.py delta_rule --batch 1 --tokens 2048 --heads 32 --kv-heads 16 --head-dim 128
+    python microbench.py gated_recurrence --batch 1 --tokens 2048 --k 4096
+    python microbench.py routed_experts --m 2048 --k 4096 --n 1792 --experts 32 --top 8 [--variant narrow]
+    python microbench.py norm_add --m 2048 --k 4096 --top 8
     LLMB_NVCC_FLAGS=-DLLMB_TRACE python microbench.py linear --m 8 --n 6144 --k 4096 --timeline
     LLMB_NVCC_FLAGS=-DLLMB_TRACE python microbench.py attention_prefill --tokens 2048 --timeline
 
@@ -150,7 +154,8 @@ def phase_sums(fn, label: str) -> int:
 
 def main(argv=None) -> int:
     p = argparse.ArgumentParser(description=__doc__.split("\n")[0])
-    p.add_argument("op", choices=["linear", "attention_decode", "attention_prefill", "rmsnorm",
+    p.add_argument("op", choices=["delta_rule", "gated_recurrence", "routed_experts", "norm_add",
+                                  "linear", "attention_decode", "attention_prefill", "rmsnorm",
                                   "swiglu", "rope", "sample"])
     p.add_argument("--m", type=int, default=8, help="rows (tokens)")
     p.add_argument("--n", type=int, default=6144)
@@ -174,6 +179,8 @@ def main(argv=None) -> int:
     p.add_argument("--temperature", type=float, default=0.0,
                    help="sample: 0 is greedy; above it the default chain (top-k 40, top-p 0.75, min-p 0.25, "
                         "repeat penalty 1.1 over the last 64) runs")
+    p.add_argument("--experts", type=int, default=32)
+    p.add_argument("--top", type=int, default=8, help="routed_experts: chosen experts; norm_add: rows a token")
     p.add_argument("--reps", type=int, default=20)
     p.add_argument("--once", action="store_true")
     p.add_argument("--timeline", action="store_true",
@@ -307,6 +314,69 @@ def main(argv=None) -> int:
         angles = torch.randn(args.context, d, device=DEV)
         run(lambda: rope_cache_write(qkv, angles, pos, seq, table, pages_per, kc, vc, hq, hkv, d), args,
             0.0, 0.0, f"rope_cache_write batch={b}")
+    elif args.op in ("delta_rule", "gated_recurrence"):
+        # `--batch` sequences bring `--tokens` tokens each (1: a decode step); the state of every sequence is read and written
+        from llm_b200 import ops
+        b, t = args.batch, args.tokens
+        n = b * t
+        seq = torch.arange(b, dtype=torch.int32, device=DEV).repeat_interleave(t)
+        cu = torch.arange(b + 1, dtype=torch.int32, device=DEV) * t
+        slots = torch.arange(b, dtype=torch.int32, device=DEV)
+        if args.op == "delta_rule":
+            H, G, D, V, K = args.heads, args.kv_heads, args.head_dim, args.head_dim, 4
+            C = 2 * G * D + H * V
+            proj = torch.randn(n, (C + H * V + 2 * H + 7) // 8 * 8, device=DEV).to(bf16)
+            taps = torch.randn(C, K, device=DEV) / 2
+            state = torch.zeros(b, (K - 1) * C + H * D * V, device=DEV)
+            rate, dt_bias, weight = -torch.ones(H, device=DEV), torch.zeros(H, device=DEV), torch.ones(V, device=DEV)
+            work = torch.empty(n, ops.delta_rule_work_width(H, G, D, V), device=DEV)
+            o, mixed = torch.empty(n, H * V, device=DEV), torch.empty(n, H * V, device=DEV, dtype=bf16)
+            moved = proj.numel() * 2 + work.numel() * 8 + o.numel() * 8 + mixed.numel() * 2 + state.numel() * 8
+            run(lambda: ops.delta_rule(proj, taps, state, seq, cu, slots, rate, dt_bias, 1e-6, weight, 1e-5, work, o, mixed,
+                                       H, G, D, V), args, moved, 6.0 * n * H * D * V,
+                f"delta_rule {b} x {t} tokens, {H}/{G} heads of {D}")
+        else:
+            channels, blocks, K = args.k, 16, 4
+            part = channels // blocks
+            wide = torch.randn(n, 2 * channels, device=DEV).to(bf16)
+            conv_w, conv_b = torch.randn(channels, K, device=DEV) / 2, torch.zeros(channels, device=DEV)
+            gate = torch.randn(blocks, part, part, device=DEV) / part ** 0.5
+            zeros, rate = torch.zeros(channels, device=DEV), -torch.ones(channels, device=DEV)
+            state = torch.zeros(b, K, channels, device=DEV)
+            out, work = torch.empty(n, channels, device=DEV, dtype=bf16), torch.empty(3, n, channels, device=DEV)
+            moved = wide.numel() * 2 + out.numel() * 2 + work.numel() * 8 + state.numel() * 8
+            run(lambda: ops.gated_recurrence(wide[:, :channels], wide[:, channels:], conv_w, conv_b, gate, zeros, gate, zeros,
+                                             rate, state, seq, cu, slots, out, 1.0, work,
+                                             single_tokens=t == 1), args, moved, 4.0 * n * channels * part,
+                f"gated_recurrence {b} x {t} tokens, {channels} channels in {blocks} blocks")
+    elif args.op == "routed_experts":
+        # `--m` tokens, width `--k`, `--experts` experts of `--n`, `--top` chosen; weights rotate only across experts
+        from llm_b200 import ops
+        n, hidden, F, E, top = args.m, args.k, args.n, args.experts, args.top
+        h = torch.randn(n, hidden, device=DEV).to(bf16)
+        router = torch.randn(E, hidden, device=DEV)
+        w_up = (torch.randn(E, 2 * F, hidden, device=DEV) * 0.02).to(bf16)
+        w_down = (torch.randn(E, hidden, F, device=DEV) * 0.02).to(bf16)
+        a = n * top
+        ids, order = torch.zeros(a, dtype=torch.int32, device=DEV), torch.zeros(a, dtype=torch.int32, device=DEV)
+        weights = torch.zeros(a, device=DEV)
+        plan = torch.zeros(ops.routed_experts_plan_ints(n, top, E), dtype=torch.int32, device=DEV)
+        act, y = torch.zeros(a, F, device=DEV, dtype=bf16), torch.zeros(a, hidden, device=DEV)
+        gathered = torch.zeros(a, hidden, device=DEV, dtype=bf16)
+        if args.variant == "narrow":
+            tactics.disable("routed_experts_wide")
+        ops.routed_experts(h, router, None, w_up, w_down, top, ids, weights, order, plan, act, y, gathered)
+        used = int(torch.unique(ids).numel())
+        moved = used * 3 * hidden * F * 2 + a * (hidden * 2 + F * 4 + hidden * 4)
+        run(lambda: ops.routed_experts(h, router, None, w_up, w_down, top, ids, weights, order, plan, act, y, gathered), args,
+            moved, 6.0 * a * hidden * F, f"routed_experts {n} tokens, {top} of {E} experts of {F} ({used} used), width {hidden}")
+    elif args.op == "norm_add":
+        from llm_b200 import ops
+        x, y = torch.randn(args.m, args.k, device=DEV), torch.randn(args.m * args.top, args.k, device=DEV)
+        g = torch.ones(args.k, device=DEV)
+        out = torch.empty(args.m, args.k, device=DEV, dtype=bf16)
+        run(lambda: ops.norm_add_(x, y, g, 1e-5, args.top, g, 1e-5, out=out, out_dtype=bf16), args,
+            args.m * args.k * (4 * args.top + 10), 0.0, f"norm_add {args.m}x{args.k}, {args.top} rows a token")
     return 0
 
 

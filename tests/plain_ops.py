@@ -308,7 +308,7 @@ def fill_(x, value):
 
 
 def delta_rule_work_width(n_heads, n_kv_heads, dim, vdim):
-    return 2 * n_kv_heads * dim + n_heads * vdim + 2 * n_heads + n_kv_heads
+    return (2 * n_kv_heads * dim + n_heads * vdim + 2 * n_heads + n_kv_heads + 3) // 4 * 4
 
 
 def delta_rule(proj, taps, state, tok_seq, cu_seqlens, slot_ids, rate, dt_bias, unit_eps, norm_weight, eps, work, o,
@@ -361,7 +361,11 @@ def routed_experts_plan_ints(n_tokens, top, n_experts):
     return n_experts + 2 + 3 * ((n_tokens * top + 31) // 32 + n_experts)
 
 
-def routed_experts(h, router, router_bias, w_up, w_down, top, ids, weights, order, plan, act, y):
+def routed_experts_wide(n_tokens, top, n_experts, hidden, intermediate, dtype):
+    return False
+
+
+def routed_experts(h, router, router_bias, w_up, w_down, top, ids, weights, order, plan, act, y, gathered=None):
     """Token by token: 32-bit router logits, the `top` largest, the softmax over them, and one row
     weight * expert(h) per choice, in the order of choice (largest logit first)."""
     n, hidden = h.shape
@@ -591,7 +595,8 @@ OPS = {"embed": embed, "scale_": scale_, "cast_sumsq": cast_sumsq, "rmsnorm": rm
        "sigmoid_attention": sigmoid_attention, "gated_recurrence": gated_recurrence,
        "sample_rows": sample_rows, "norm_add_": norm_add_, "gelu_": gelu_, "sigmoid_gate_": sigmoid_gate_,
        "add_terms_": add_terms_, "fill_": fill_, "delta_rule": delta_rule, "delta_rule_work_width": delta_rule_work_width,
-       "routed_experts": routed_experts, "routed_experts_plan_ints": routed_experts_plan_ints}
+       "routed_experts": routed_experts, "routed_experts_plan_ints": routed_experts_plan_ints,
+       "routed_experts_wide": routed_experts_wide}
 
 
 def install(monkeypatch):

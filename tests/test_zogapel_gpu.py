@@ -302,7 +302,8 @@ def _experts(fn, h, router, bias, w_up, w_down, top):
     plan = torch.zeros(ops.routed_experts_plan_ints(n, top, E), dtype=torch.int32, device=DEV)
     act = torch.zeros((a, w_down.shape[2]), dtype=h.dtype, device=DEV)
     y = torch.zeros((a, hidden), device=DEV)
-    fn(h, router, bias, w_up, w_down, top, ids, weights, order, plan, act, y)
+    gathered = torch.zeros((a, hidden), dtype=h.dtype, device=DEV)
+    fn(h, router, bias, w_up, w_down, top, ids, weights, order, plan, act, y, gathered)
     return ids, weights, y
 
 
@@ -317,9 +318,11 @@ def test_routed_experts(dtype, case):
     bias = (0.7 * torch.randn(E, generator=gen)).to(DEV)
     w_up = (torch.randn((E, 2 * F, hidden), generator=gen) / hidden ** 0.5).to(dtype).to(DEV)
     w_down = (torch.randn((E, hidden, F), generator=gen) / F ** 0.5).to(dtype).to(DEV)
-    for n in (1, 2, 33, 70, 300):
+    for n in (1, 2, 33, 70, 300, 1000):                      # the larger steps of bfloat16 take the tiles of 128 rows
         wide = torch.randn((n, hidden + 8), generator=gen).to(dtype).to(DEV)
         h = wide[:, :hidden]
+        if dtype == torch.bfloat16 and hidden % 8 == 0 and F % 8 == 0:
+            assert ops.routed_experts_wide(n, top, E, hidden, F, dtype) == (n * top >= 32 * E)
         for b in (bias, None):
             ids, weights, y = _experts(ops.routed_experts, h, router, b, w_up, w_down, top)
             want_ids, want_weights, want_y = _experts(plain_ops.routed_experts, h, router, b, w_up, w_down, top)
@@ -328,6 +331,35 @@ def test_routed_experts(dtype, case):
             _close(weights, want_weights, torch.float32, (case, n, "weights"))
             _close(y, want_y, dtype, (case, n, "rows"))
             assert torch.allclose(weights.view(n, top).sum(-1), torch.ones(n, device=DEV), atol=1e-5)
+
+
+def test_routed_experts_on_wide_tiles_agree_with_narrow_ones():
+    """The same step through the tiles of 128 rows and, with those switched off, through the tiles of 32: equal up
+    to the order of the sums; experts with no row, one row, and more rows than a tile holds."""
+    ops = _ops()
+    from llm_b200.ops import tactics
+    hidden, F, E, top, n = 192, 72, 6, 2, 700
+    gen = torch.Generator().manual_seed(3)
+    router = (3.0 * torch.randn((E, hidden), generator=gen) / hidden ** 0.5).to(DEV)
+    bias = torch.tensor([2.0, 2.0, 0.0, -9.0, -60.0, 1.0], device=DEV)         # expert 4 is never chosen, expert 3 rarely
+    w_up = (torch.randn((E, 2 * F, hidden), generator=gen) / hidden ** 0.5).bfloat16().to(DEV)
+    w_down = (torch.randn((E, hidden, F), generator=gen) / F ** 0.5).bfloat16().to(DEV)
+    h = torch.randn((n, hidden), generator=gen).bfloat16().to(DEV)
+    assert ops.routed_experts_wide(n, top, E, hidden, F, torch.bfloat16)
+    ids, weights, y = _experts(ops.routed_experts, h, router, bias, w_up, w_down, top)
+    counts = torch.bincount(ids.long(), minlength=E).tolist()
+    assert counts[4] == 0 and max(counts) > 256 and 0 < counts[3] < 128, counts
+    tactics.disable("routed_experts_wide")
+    try:
+        assert not ops.routed_experts_wide(n, top, E, hidden, F, torch.bfloat16)
+        ids_narrow, weights_narrow, y_narrow = _experts(ops.routed_experts, h, router, bias, w_up, w_down, top)
+    finally:
+        tactics.enable("routed_experts_wide")
+    torch.cuda.synchronize()
+    ops.check_device_status()
+    assert torch.equal(ids, ids_narrow) and torch.equal(weights, weights_narrow)
+    _close(y, y_narrow, torch.bfloat16, "rows")
+    assert float((y - y_narrow).abs().max()) <= 2e-2 * float(y_narrow.abs().max())
 
 
 def test_routed_experts_choice_ties_and_batch_independence():
