@@ -1,14 +1,16 @@
 // A feed-forward of routed experts: every token is sent to the `top` experts with the largest router
 // logits, its result is the sum of their results weighted by the softmax over the chosen logits.
 //
-// router   one block per token: logits = W_r h + b in 32-bit (W_r and b are held in 32-bit; h is the
-//          normed input in the run's dtype), the `top` largest (the lower index wins a tie), softmax over
-//          them. An assignment is a pair (token, k): index t * top + k.
-// plan     one block: counts the assignments of every expert, lists them grouped by expert (inside an
-//          expert in rising order, so the plan is a function of the routing alone) and cuts every
-//          expert's list into tiles of 32 (or, for the tcgen05 products, 128) rows: (expert, first row, rows) per tile. Nothing of this
-//          reaches the host: the product kernels are launched with the largest possible tile count
-//          and blocks beyond the plan's count leave at once, so a step can be captured and replayed.
+// router   logits = W_r h + b in 32-bit (W_r and b are held in 32-bit; h is the normed input in the run's
+//          dtype), the `top` largest (the lower index wins a tie), softmax over them. One block of 16 warps per token (a warp an
+//          expert at a time), or, for steps of 512 tokens and more, four warps per four tokens (a weight row is
+//          fetched once for the four). An
+//          assignment is a pair (token, k): index t * top + k.
+// plan     counts the assignments of every expert, lists them grouped by expert (inside an expert in rising
+//          order, so the plan is a function of the routing alone) and cuts every expert's list into tiles of 32
+//          (or, for the tcgen05 products, 128) rows: (expert, first row, rows) per tile. Nothing of this reaches
+//          the host: the product kernels are launched with the largest possible tile count and blocks beyond the
+//          plan's count leave at once, so a step can be captured and replayed.
 // up       for every tile: act[s, :] = silu(W_gate,e h_t) * (W_up,e h_t) for the rows s of the sorted list
 //          (h_t gathered through the list), one weight matrix [2 F, K] per expert (gate rows, then up).
 // down     for every tile: y[t * top + k, :] = weight[t, k] * (W_down,e act[s, :]), 32-bit, written at the
@@ -35,55 +37,106 @@ LLMB_DEFINE_LAST_ERROR(llmb_routed_experts)
 constexpr int MAX_TOP = 16;
 constexpr int TILE_M = 32;
 
-template <typename T>
-__global__ void __launch_bounds__(128)
+__device__ __forceinline__ void load4(const float* p, float (&x)[4]) {
+    float4 v = *reinterpret_cast<const float4*>(p);
+    x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
+}
+__device__ __forceinline__ void load4(const __nv_bfloat16* p, float (&x)[4]) {
+    uint2 v = *reinterpret_cast<const uint2*>(p);
+    float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.x));
+    float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.y));
+    x[0] = lo.x; x[1] = lo.y; x[2] = hi.x; x[3] = hi.y;
+}
+
+// A block takes TOK tokens: a weight row fetched once serves all of them. A token's sum runs in the same order
+// whatever TOK is (a lane's elements in rising order, then the lanes as a butterfly).
+template <typename T, int TOK>
+__global__ void __launch_bounds__(512)
 router_kernel(const T* __restrict__ h, int ld, const float* __restrict__ w, const float* __restrict__ bias,
-              int hidden, int E, int top, int* __restrict__ ids, float* __restrict__ weights) {
-    extern __shared__ float logits[];      // [E]
+              int hidden, int E, int top, int* __restrict__ ids, float* __restrict__ weights, int n_tokens, int vectors) {
+    extern __shared__ float logits[];      // [TOK][E]
     griddep_launch();
     griddep_wait();
-    size_t t = blockIdx.x;
+    size_t t0 = (size_t)blockIdx.x * TOK;
     int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int e = warp; e < E; e += 4) {
-        float acc = 0.f;
-        for (int c = lane; c < hidden; c += 32) acc = fmaf(w[(size_t)e * hidden + c], to_float(h[t * ld + c]), acc);
-        acc = warp_sum(acc);
-        if (lane == 0) logits[e] = acc + (bias ? bias[e] : 0.f);
+    const T* rows[TOK];
+#pragma unroll
+    for (int i = 0; i < TOK; ++i) rows[i] = h + min(t0 + i, (size_t)n_tokens - 1) * ld;
+    for (int e = warp; e < E; e += blockDim.x >> 5) {
+        float acc[TOK];
+#pragma unroll
+        for (int i = 0; i < TOK; ++i) acc[i] = 0.f;
+        const float* we = w + (size_t)e * hidden;
+        if (vectors) {
+            // four elements a lane a step (width, row length and addresses allow it: a property of the model, so a
+            // token's sum has one order in every step)
+#pragma unroll 2
+            for (int c = 4 * lane; c < hidden; c += 128) {
+                float wv[4];
+                load4(we + c, wv);
+#pragma unroll
+                for (int i = 0; i < TOK; ++i) {
+                    float x[4];
+                    load4(rows[i] + c, x);
+                    acc[i] = fmaf(wv[0], x[0], acc[i]);
+                    acc[i] = fmaf(wv[1], x[1], acc[i]);
+                    acc[i] = fmaf(wv[2], x[2], acc[i]);
+                    acc[i] = fmaf(wv[3], x[3], acc[i]);
+                }
+            }
+        } else {
+#pragma unroll 4
+            for (int c = lane; c < hidden; c += 32) {
+                float wv = we[c];
+#pragma unroll
+                for (int i = 0; i < TOK; ++i) acc[i] = fmaf(wv, to_float(rows[i][c]), acc[i]);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < TOK; ++i) {
+            float total = warp_sum(acc[i]);
+            if (lane == 0) logits[i * E + e] = total + (bias ? bias[e] : 0.f);
+        }
     }
     __syncthreads();
-    if (threadIdx.x != 0) return;
+    if (threadIdx.x >= TOK || t0 + threadIdx.x >= (size_t)n_tokens) return;
+    size_t t = t0 + threadIdx.x;
+    float* mine = logits + threadIdx.x * E;
     float chosen[MAX_TOP];
     for (int k = 0; k < top; ++k) {
         int best = 0;
         float value = -INFINITY;
         for (int e = 0; e < E; ++e)
-            if (logits[e] > value) { value = logits[e]; best = e; }
+            if (mine[e] > value) { value = mine[e]; best = e; }
         chosen[k] = value;
         ids[t * top + k] = best;
-        logits[best] = -INFINITY;
+        mine[best] = -INFINITY;
     }
     float total = 0.f, largest = chosen[0];
     for (int k = 0; k < top; ++k) { chosen[k] = expf(chosen[k] - largest); total += chosen[k]; }
     for (int k = 0; k < top; ++k) weights[t * top + k] = chosen[k] / total;
 }
 
-// plan: [0, E] offsets | [E + 1] tile count | then three arrays of max_tiles: expert, first row, rows
-__global__ void __launch_bounds__(1024)
+// plan: [0, E] offsets | [E + 1] tile count | then three arrays of max_tiles: expert, first row, rows.
+// Several blocks: every block counts all assignments (it needs every expert's offset), block 0 writes the offsets
+// and the tiles, and block b lists the assignments of the experts b, b + blocks, ..: its warps take consecutive
+// segments of the assignments, count their matches, and place them behind the segments before.
+constexpr int PLAN_THREADS = 1024;
+__global__ void __launch_bounds__(PLAN_THREADS)
 plan_kernel(const int* __restrict__ ids, int n_assign, int E, int* __restrict__ sorted, int* __restrict__ plan,
             int max_tiles, int tile_m) {
-    extern __shared__ int shared[];        // counts [E] | offsets [E + 1] | tile bases [E + 1]
+    extern __shared__ int shared[];        // counts [E] | offsets [E + 1] | tile bases [E + 1] | a count per warp [32]
     int* counts = shared;
     int* offsets = shared + E;
     int* bases = shared + 2 * E + 1;
+    int* warp_counts = shared + 3 * E + 2;
     griddep_launch();
     griddep_wait();
-    int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
-    for (int e = warp; e < E; e += n_warps) {
-        int count = 0;
-        for (int i = lane; i < n_assign; i += 32) count += ids[i] == e;
-        for (int offset = 16; offset > 0; offset >>= 1) count += __shfl_xor_sync(0xffffffffu, count, offset);
-        if (lane == 0) counts[e] = count;
-    }
+    int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr int n_warps = PLAN_THREADS / 32;
+    for (int e = threadIdx.x; e < E; e += PLAN_THREADS) counts[e] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < n_assign; i += PLAN_THREADS) atomicAdd(&counts[ids[i]], 1);
     __syncthreads();
     if (threadIdx.x == 0) {
         int at = 0, tiles = 0;
@@ -95,31 +148,45 @@ plan_kernel(const int* __restrict__ ids, int n_assign, int E, int* __restrict__ 
         }
         offsets[E] = at;
         bases[E] = tiles;
-        plan[E + 1] = tiles < max_tiles ? tiles : max_tiles;
+        if (blockIdx.x == 0) plan[E + 1] = tiles < max_tiles ? tiles : max_tiles;
     }
     __syncthreads();
-    for (int e = threadIdx.x; e <= E; e += blockDim.x) plan[e] = offsets[e];
-    int* tile_expert = plan + E + 2;
-    int* tile_first = tile_expert + max_tiles;
-    int* tile_rows = tile_first + max_tiles;
-    for (int e = threadIdx.x; e < E; e += blockDim.x) {
-        int n = counts[e];
-        for (int i = 0, tile = bases[e]; i < n && tile < max_tiles; i += tile_m, ++tile) {
-            tile_expert[tile] = e;
-            tile_first[tile] = offsets[e] + i;
-            tile_rows[tile] = min(tile_m, n - i);
+    if (blockIdx.x == 0) {
+        for (int e = threadIdx.x; e <= E; e += PLAN_THREADS) plan[e] = offsets[e];
+        int* tile_expert = plan + E + 2;
+        int* tile_first = tile_expert + max_tiles;
+        int* tile_rows = tile_first + max_tiles;
+        for (int e = threadIdx.x; e < E; e += PLAN_THREADS) {
+            int n = counts[e];
+            for (int i = 0, tile = bases[e]; i < n && tile < max_tiles; i += tile_m, ++tile) {
+                tile_expert[tile] = e;
+                tile_first[tile] = offsets[e] + i;
+                tile_rows[tile] = min(tile_m, n - i);
+            }
         }
     }
+    int segment = ((n_assign + n_warps - 1) / n_warps + 31) / 32 * 32;
+    int begin = min(warp * segment, n_assign), end = min(begin + segment, n_assign);
     const unsigned below = (1u << lane) - 1u;
-    for (int e = warp; e < E; e += n_warps) {
-        int at = offsets[e];
-        for (int i0 = 0; i0 < n_assign; i0 += 32) {
+    for (int e = blockIdx.x; e < E; e += gridDim.x) {
+        if (counts[e] == 0) continue;                 // (the same answer in every thread)
+        int matches = 0;
+        for (int i0 = begin; i0 < end; i0 += 32) {
             int i = i0 + lane;
-            bool mine = i < n_assign && ids[i] == e;
+            matches += __popc(__ballot_sync(0xffffffffu, i < end && ids[i] == e));
+        }
+        if (lane == 0) warp_counts[warp] = matches;
+        __syncthreads();
+        int at = offsets[e];
+        for (int w = 0; w < warp; ++w) at += warp_counts[w];
+        for (int i0 = begin; i0 < end; i0 += 32) {
+            int i = i0 + lane;
+            bool mine = i < end && ids[i] == e;
             unsigned mask = __ballot_sync(0xffffffffu, mine);
             if (mine) sorted[at + __popc(mask & below)] = i;
             at += __popc(mask);
         }
+        __syncthreads();
     }
 }
 
@@ -556,6 +623,7 @@ LLMB_EXPORT int llmb_routed_experts(const void* h, int ld, int dtype, const floa
     int max_tiles = (n_assign + TILE_M - 1) / TILE_M + E;
     dim3 grid_up((F + BN - 1) / BN, max_tiles), grid_down((hidden + BN - 1) / BN, max_tiles);
     long long up_stride = 2LL * F * hidden, down_stride = (long long)hidden * F;
+    int router_vectors = hidden % 4 == 0 && ld % 4 == 0 && ((size_t)h % 16) == 0 && ((size_t)router % 16) == 0;
     bool aligned = ld % 8 == 0 && ((size_t)h % 16) == 0 && ((size_t)w_up % 16) == 0 && ((size_t)w_down % 16) == 0 &&
                    ((size_t)act % 16) == 0;
     bool wide_tiles = tensor_cores >= 2 && dtype == LLMB_DTYPE_BF16 && gathered && hidden % 8 == 0 && F % 8 == 0 && aligned &&
@@ -564,10 +632,17 @@ LLMB_EXPORT int llmb_routed_experts(const void* h, int ld, int dtype, const floa
     int tile_m = wide_tiles ? wide::GM : TILE_M;
 #define LLMB_EXPERTS(T)                                                                                            \
     do {                                                                                                           \
-        LLMB_CUDA(llmb::launch(router_kernel<T>, dim3(n_tokens), dim3(128), sizeof(float) * E, stream, true,       \
-                               (const T*)h, ld, router, router_bias, hidden, E, top, ids, weights));               \
-        LLMB_CUDA(llmb::launch(plan_kernel, dim3(1), dim3(1024), sizeof(int) * (3 * E + 2), stream, true,          \
-                               (const int*)ids, n_assign, E, sorted, plan, max_tiles, tile_m));                    \
+        if (n_tokens >= 512)                                                                                       \
+            LLMB_CUDA(llmb::launch(router_kernel<T, 4>, dim3((n_tokens + 3) / 4), dim3(128), sizeof(float) * 4 * E, \
+                                   stream, true, (const T*)h, ld, router, router_bias, hidden, E, top, ids,       \
+                                   weights, n_tokens, router_vectors));                                            \
+        else                                                                                                       \
+            LLMB_CUDA(llmb::launch(router_kernel<T, 1>, dim3(n_tokens), dim3(512), sizeof(float) * E, stream,     \
+                                   true, (const T*)h, ld, router, router_bias, hidden, E, top, ids, weights,       \
+                                   n_tokens, router_vectors));                                                     \
+        LLMB_CUDA(llmb::launch(plan_kernel, dim3(E < 64 ? E : 64), dim3(PLAN_THREADS),                             \
+                               sizeof(int) * (3 * E + 2 + 32), stream, true, (const int*)ids, n_assign, E, sorted, \
+                               plan, max_tiles, tile_m));                                                          \
     } while (0)
     if (dtype == LLMB_DTYPE_F32) LLMB_EXPERTS(float);
     else if (dtype == LLMB_DTYPE_BF16) LLMB_EXPERTS(__nv_bfloat16);
