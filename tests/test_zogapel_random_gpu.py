@@ -66,8 +66,8 @@ def draw_config(rng) -> dict:
 
 def close(got, want, dtype, sure=None) -> bool:
     got, want = got.float().cpu(), want.float()
-    if dtype == torch.float32:
-        return bool(torch.allclose(got, want, atol=6e-4, rtol=2e-4))
+    if dtype == torch.float32:              # rounding goes with the size of the logits (an embedding scale of 12 makes them large)
+        return bool(torch.allclose(got, want, atol=max(6e-4, 2e-5 * float(want.max() - want.min())), rtol=2e-4))
     if got.dim() == 1:
         got, want = got[None], want[None]
         sure = None if sure is None else torch.as_tensor(sure).reshape(1)
@@ -95,8 +95,10 @@ def test_random_configuration(tmp_path, case):
     for s in seqs:
         per_layer = []
         expected.append(plain.forward(config, weights, s, margins=per_layer))
-        # bfloat16: positions at which an expert was chosen by less than rounding reaches are not compared
-        margins.append(torch.stack(per_layer).min(dim=0).values > 0.15 if per_layer else torch.ones(len(s), dtype=torch.bool))
+        # bfloat16: from the first position on at which an expert was chosen by less than rounding reaches, a sequence is
+        # not compared (another expert there changes what every later position reads from the state and the cache)
+        margins.append(torch.cummin(torch.stack(per_layer).min(dim=0).values, dim=0).values > 0.15 if per_layer
+                       else torch.ones(len(s), dtype=torch.bool))
     for dtype in (torch.float32, torch.bfloat16):
         sure = [None if dtype == torch.float32 else m for m in margins]
         engine = Engine(load_model(folder, dtype, DEV), max_tokens=64 * 7 * len(seqs), max_slots=len(seqs))
