@@ -618,7 +618,7 @@ LLMB_EXPORT int llmb_routed_experts(const void* h, int ld, int dtype, const floa
     if (n_tokens == 0) return LLMB_OK;
     LLMB_REQUIRE(hidden > 0 && F > 0 && E > 0 && top > 0 && top <= E && top <= MAX_TOP,
                  "routed_experts: %d of %d experts (at most %d are chosen)", top, E, MAX_TOP);
-    LLMB_REQUIRE(E <= 4096, "routed_experts: %d experts (up to 4096 are built)", E);
+    LLMB_REQUIRE(E <= 2048, "routed_experts: %d experts (up to 2048 are built)", E);
     int n_assign = n_tokens * top;
     int max_tiles = (n_assign + TILE_M - 1) / TILE_M + E;
     dim3 grid_up((F + BN - 1) / BN, max_tiles), grid_down((hidden + BN - 1) / BN, max_tiles);
