@@ -90,32 +90,68 @@ __device__ __forceinline__ float gelu_tanh(float z) {
     return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
 
+// 16 bytes a thread where the address allows it (`vectors`), the last elements one by one
 template <typename T>
-__global__ void gelu_kernel(T* __restrict__ a, long long n) {
+__global__ void gelu_kernel(T* __restrict__ a, long long n, int vectors) {
     griddep_launch();
     griddep_wait();
+    constexpr int VEC = 16 / sizeof(T);
     long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (vectors) {
+        long long first = i * VEC;
+        if (first + VEC <= n) {
+            uint4 raw = reinterpret_cast<const uint4*>(a)[i];
+            T* e = reinterpret_cast<T*>(&raw);
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) e[j] = from_float<T>(gelu_tanh(to_float(e[j])));
+            reinterpret_cast<uint4*>(a)[i] = raw;
+        } else {
+            for (long long k = first; k < n; ++k) a[k] = from_float<T>(gelu_tanh(to_float(a[k])));
+        }
+        return;
+    }
     if (i < n) a[i] = from_float<T>(gelu_tanh(to_float(a[i])));
 }
 
 LLMB_EXPORT int llmb_gelu(void* a, int dtype, long long n, cudaStream_t stream) {
     if (n == 0) return LLMB_OK;
     LLMB_REQUIRE(n > 0 && a, "gelu: bad size");
-    unsigned blocks = (unsigned)((n + 255) / 256);
-    if (dtype == LLMB_DTYPE_F32) LLMB_CUDA(llmb::launch(gelu_kernel<float>, dim3(blocks), dim3(256), 0, stream, true, (float*)a, n));
+    int vectors = ((size_t)a % 16) == 0;
+    long long per_thread = vectors ? (dtype == LLMB_DTYPE_F32 ? 4 : 8) : 1;
+    long long threads = (n + per_thread - 1) / per_thread;
+    unsigned blocks = (unsigned)((threads + 255) / 256);
+    if (dtype == LLMB_DTYPE_F32)
+        LLMB_CUDA(llmb::launch(gelu_kernel<float>, dim3(blocks), dim3(256), 0, stream, true, (float*)a, n, vectors));
     else if (dtype == LLMB_DTYPE_BF16)
-        LLMB_CUDA(llmb::launch(gelu_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, true, (__nv_bfloat16*)a, n));
+        LLMB_CUDA(llmb::launch(gelu_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, true, (__nv_bfloat16*)a, n, vectors));
     else return fail(LLMB_ERR_ARGUMENT, "gelu: unknown dtype %d", dtype);
     return check_launch("gelu");
 }
 LLMB_PACKED(llmb_gelu)
 
+// `vectors`: 16 bytes a thread (width, both strides and both addresses allow it)
 template <typename T>
 __global__ void sigmoid_gate_kernel(T* __restrict__ out, int out_stride, const T* __restrict__ gate, int gate_stride,
-                                    int width, long long total) {
+                                    int width, long long total, int vectors) {
     griddep_launch();
     griddep_wait();
+    constexpr int VEC = 16 / sizeof(T);
     long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (vectors) {
+        int per_row = width / VEC;
+        if (i >= total / VEC) return;
+        long long t = i / per_row;
+        int c = (int)(i % per_row) * VEC;
+        uint4 g_raw = *reinterpret_cast<const uint4*>(gate + t * gate_stride + c);
+        uint4* dst = reinterpret_cast<uint4*>(out + t * out_stride + c);
+        uint4 v_raw = *dst;
+        const T* g = reinterpret_cast<const T*>(&g_raw);
+        T* v = reinterpret_cast<T*>(&v_raw);
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) v[j] = from_float<T>(to_float(v[j]) / (1.0f + expf(-to_float(g[j]))));
+        *dst = v_raw;
+        return;
+    }
     if (i >= total) return;
     long long t = i / width;
     int c = (int)(i % width);
@@ -129,13 +165,17 @@ LLMB_EXPORT int llmb_sigmoid_gate(void* out, int out_stride, const void* gate, i
     if (n_rows == 0) return LLMB_OK;
     LLMB_REQUIRE(width > 0 && out_stride >= width && gate_stride >= width, "sigmoid_gate: bad widths");
     long long total = (long long)n_rows * width;
-    unsigned blocks = (unsigned)((total + 255) / 256);
+    int vec = dtype == LLMB_DTYPE_F32 ? 4 : 8;
+    int vectors = width % vec == 0 && out_stride % vec == 0 && gate_stride % vec == 0 && ((size_t)out % 16) == 0 &&
+                  ((size_t)gate % 16) == 0;
+    long long threads = vectors ? total / vec : total;
+    unsigned blocks = (unsigned)((threads + 255) / 256);
     if (dtype == LLMB_DTYPE_F32)
         LLMB_CUDA(llmb::launch(sigmoid_gate_kernel<float>, dim3(blocks), dim3(256), 0, stream, true, (float*)out, out_stride,
-                               (const float*)gate, gate_stride, width, total));
+                               (const float*)gate, gate_stride, width, total, vectors));
     else if (dtype == LLMB_DTYPE_BF16)
         LLMB_CUDA(llmb::launch(sigmoid_gate_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, true,
-                               (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)gate, gate_stride, width, total));
+                               (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)gate, gate_stride, width, total, vectors));
     else return fail(LLMB_ERR_ARGUMENT, "sigmoid_gate: unknown dtype %d", dtype);
     return check_launch("sigmoid_gate");
 }
