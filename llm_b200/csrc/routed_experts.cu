@@ -399,9 +399,12 @@ namespace wide {
 
 using namespace llmb::tc;
 
-constexpr int GM = 128, GN = 128, GK = 64, G_THREADS = 192, G_STAGES = 3;
-constexpr int A_BYTES = GM * GK * 2, B_BYTES = GN * GK * 2;
-constexpr size_t G_SMEM = 1024 + (size_t)G_STAGES * (A_BYTES + B_BYTES) + (2 * G_STAGES + 1) * 8 + 16;
+constexpr int GM = 128, GK = 64, G_THREADS = 192;
+constexpr int A_BYTES = GM * GK * 2;
+// tiles of 128 columns: a ring of three stages, two blocks an SM; tiles of 256 columns (two thirds of the operand bytes
+// per product): a ring of four, one block an SM
+__host__ __device__ constexpr int stages_of(int gn) { return gn == 128 ? 3 : 4; }
+__host__ __device__ constexpr size_t smem_of(int gn) { return 1024 + (size_t)stages_of(gn) * (A_BYTES + gn * GK * 2) + (2 * stages_of(gn) + 1) * 8 + 16; }
 
 // Xs[s, :] = h[sorted[s] / top, :]: the rows of h in the order of the plan (16 bytes a thread a time).
 __global__ void __launch_bounds__(256)
@@ -419,17 +422,18 @@ gather_rows_kernel(const __nv_bfloat16* __restrict__ h, int ld, int top, const i
 }
 
 // One block: the tile `blockIdx.y` of the plan (an expert's rows [first, first + rows) of the sorted list, at most
-// 128) times the output columns [blockIdx.x * (GLU ? 64 : 128), ..) of that expert. A: [rows of the list, K] behind
+// 128) times GN accumulator columns: the output columns [blockIdx.x * (GLU ? GN / 2 : GN), ..) of that expert. A: [rows of the list, K] behind
 // map_a. B: every expert's matrix stacked, [E * b_rows, K] behind map_b; GLU: an expert's b_rows = 2 N rows are N
-// gate rows, then N up rows, and a stage holds 64 gate rows and the 64 up rows of the same features, so that the
-// accumulator's columns 0..63 are gates and 64..127 the ups. Warp 0: TMA producer. Warp 1: tensor memory and the
+// gate rows, then N up rows, and a stage holds GN / 2 gate rows and the GN / 2 up rows of the same features, so that the
+// accumulator's first half are gates and its second half the ups. Warp 0: TMA producer. Warp 1: tensor memory and the
 // products. Warps 2..5: epilogue, a thread a row. Every wait is bounded and reports through `status`.
-template <bool GLU>
-__global__ void __launch_bounds__(G_THREADS, 2)
+template <bool GLU, int GN>
+__global__ void __launch_bounds__(G_THREADS, GN == 128 ? 2 : 1)
 expert_product_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                            const int* __restrict__ plan, int E, int max_tiles, int b_rows, int N, int n_kblocks,
                            __nv_bfloat16* __restrict__ act, float* __restrict__ y, const int* __restrict__ sorted,
                            const float* __restrict__ weights, int* status) {
+    constexpr int G_STAGES = stages_of(GN), B_BYTES = GN * GK * 2;
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     unsigned char* a_tiles = base;
@@ -492,7 +496,7 @@ expert_product_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            // instruction descriptor: D 32-bit, A and B bfloat16, both K-major, N = 128, M = 128
+            // instruction descriptor: D 32-bit, A and B bfloat16, both K-major, N = GN, M = 128
             constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(GN >> 3) << 17) | ((uint32_t)(GM >> 4) << 24);
             const uint64_t a_desc0 = smem_desc(smem_u32(a_tiles)), b_desc0 = smem_desc(smem_u32(b_tiles));
             int s = 0;
@@ -610,7 +614,7 @@ LLMB_EXPORT long long llmb_routed_experts_plan_ints(int n_tokens, int top, int E
 // then up rows) and w_down [E, hidden, F] in `dtype`; ids int32 [T * top], weights float32 [T * top], sorted
 // int32 [T * top], plan int32 [plan_ints]; act [T * top, F] in `dtype`; y float32 [T * top, hidden]. `tensor_cores`:
 // 0 CUDA cores only, 1 also the mma.sync tiles, 2 also the tcgen05 tiles of 128 rows, which need `gathered`
-// (bfloat16 [T * top, hidden] scratch) and are taken when the step has that scratch.
+// (bfloat16 [T * top, hidden] scratch) and are taken when the step has that scratch, 3: those with 256 accumulator columns.
 LLMB_EXPORT int llmb_routed_experts(const void* h, int ld, int dtype, const float* router, const float* router_bias,
                                     const void* w_up, const void* w_down, int* ids, float* weights, int* sorted,
                                     int* plan, void* act, float* y, void* gathered, int n_tokens, int hidden, int F,
@@ -652,10 +656,17 @@ LLMB_EXPORT int llmb_routed_experts(const void* h, int ld, int dtype, const floa
     if (wide_tiles) {
         typedef __nv_bfloat16 B;
         using namespace wide;
+        // tiles of 256 columns for long lists (measured at width 4096, 8 of 32 experts of 1792: 3.65 against 3.86 ms at 8,192
+        // tokens, equal at 2,048, behind at width 2048) where the products are wide enough for them
+        bool wide256 = tensor_cores >= 3 && F >= 128 && hidden >= 256 && (long long)n_assign >= 1024LL * E;
+        int GN = wide256 ? 256 : 128;
+        size_t smem = smem_of(GN);
         static bool configured = false;
         if (!configured) {
-            LLMB_CUDA(cudaFuncSetAttribute(expert_product_wide_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)G_SMEM));
-            LLMB_CUDA(cudaFuncSetAttribute(expert_product_wide_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)G_SMEM));
+            LLMB_CUDA(cudaFuncSetAttribute(expert_product_wide_kernel<true, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_of(128)));
+            LLMB_CUDA(cudaFuncSetAttribute(expert_product_wide_kernel<false, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_of(128)));
+            LLMB_CUDA(cudaFuncSetAttribute(expert_product_wide_kernel<true, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_of(256)));
+            LLMB_CUDA(cudaFuncSetAttribute(expert_product_wide_kernel<false, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_of(256)));
             configured = true;
         }
         int* status_dev = nullptr;
@@ -673,12 +684,14 @@ LLMB_EXPORT int llmb_routed_experts(const void* h, int ld, int dtype, const floa
         int gather_blocks = (int)((vectors + 255) / 256 < 148 * 8 ? (vectors + 255) / 256 : 148 * 8);
         LLMB_CUDA(llmb::launch(gather_rows_kernel, dim3(gather_blocks), dim3(256), 0, stream, true, (const B*)h, ld, top,
                                (const int*)sorted, n_assign, hidden, (B*)gathered));
-        LLMB_CUDA(llmb::launch(expert_product_wide_kernel<true>, dim3((F + GN / 2 - 1) / (GN / 2), tiles), dim3(G_THREADS), G_SMEM,
-                               stream, true, map_x, map_up, (const int*)plan, E, max_tiles, 2 * F, F, (hidden + GK - 1) / GK,
-                               (B*)act, (float*)nullptr, (const int*)sorted, (const float*)nullptr, status_dev));
-        LLMB_CUDA(llmb::launch(expert_product_wide_kernel<false>, dim3((hidden + GN - 1) / GN, tiles), dim3(G_THREADS), G_SMEM,
-                               stream, true, map_act, map_down, (const int*)plan, E, max_tiles, hidden, hidden,
-                               (F + GK - 1) / GK, (B*)nullptr, y, (const int*)sorted, (const float*)weights, status_dev));
+        auto up = wide256 ? expert_product_wide_kernel<true, 256> : expert_product_wide_kernel<true, 128>;
+        auto down = wide256 ? expert_product_wide_kernel<false, 256> : expert_product_wide_kernel<false, 128>;
+        LLMB_CUDA(llmb::launch(up, dim3((F + GN / 2 - 1) / (GN / 2), tiles), dim3(G_THREADS), smem, stream, true, map_x, map_up,
+                               (const int*)plan, E, max_tiles, 2 * F, F, (hidden + GK - 1) / GK, (B*)act, (float*)nullptr,
+                               (const int*)sorted, (const float*)nullptr, status_dev));
+        LLMB_CUDA(llmb::launch(down, dim3((hidden + GN - 1) / GN, tiles), dim3(G_THREADS), smem, stream, true, map_act, map_down,
+                               (const int*)plan, E, max_tiles, hidden, hidden, (F + GK - 1) / GK, (B*)nullptr, y,
+                               (const int*)sorted, (const float*)weights, status_dev));
     } else if (tc) {
         typedef __nv_bfloat16 B;
         LLMB_CUDA(llmb::launch(expert_product_tc_kernel<true>, dim3((F + 63) / 64, max_tiles), dim3(128), 0, stream, true,

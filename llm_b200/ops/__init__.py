@@ -626,7 +626,8 @@ def routed_experts(h, router, router_bias, w_up, w_down, top: int, ids, weights,
     wide = gathered is not None and routed_experts_wide(n, top, E, hidden, F, h.dtype)
     if wide and (gathered.dtype != h.dtype or gathered.numel() < a * hidden or not gathered.is_contiguous()):
         raise KernelError(f"routed_experts: gathered must be contiguous {h.dtype} with at least {a * hidden} elements")
-    level = 0 if tactics.is_disabled("routed_experts_tc") else (2 if wide else 1)
+    level = 0 if tactics.is_disabled("routed_experts_tc") else (
+        (2 if tactics.is_disabled("routed_experts_wide256") else 3) if wide else 1)
     _call("routed_experts", "llmb_routed_experts", _ptr(h), _c_int(h.stride(0)), _c_int(_code(h.dtype)), _ptr(router),
           _ptr(router_bias), _ptr(w_up), _ptr(w_down), _ptr(ids), _ptr(weights), _ptr(order), _ptr(plan), _ptr(act),
           _ptr(y), _ptr(gathered if wide else None), _c_int(n), _c_int(hidden), _c_int(F), _c_int(E), _c_int(top),

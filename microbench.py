@@ -7,7 +7,7 @@
     python microbench.py sample --batch 8 --n 128256 [--temperature 0.7]
     python microbench.py delta_rule --batch 1 --tokens 2048 --heads 32 --kv-heads 16 --head-dim 128
     python microbench.py gated_recurrence --batch 1 --tokens 2048 --k 4096
-    python microbench.py routed_experts --m 2048 --k 4096 --n 1792 --experts 32 --top 8 [--variant narrow]
+    python microbench.py routed_experts --m 2048 --k 4096 --n 1792 --experts 32 --top 8 [--variant narrow|wide128]
     python microbench.py norm_add --m 2048 --k 4096 --top 8
     LLMB_NVCC_FLAGS=-DLLMB_TRACE python microbench.py linear --m 8 --n 6144 --k 4096 --timeline
     LLMB_NVCC_FLAGS=-DLLMB_TRACE python microbench.py attention_prefill --tokens 2048 --timeline
@@ -365,6 +365,8 @@ def main(argv=None) -> int:
         gathered = torch.zeros(a, hidden, device=DEV, dtype=bf16)
         if args.variant == "narrow":
             tactics.disable("routed_experts_wide")
+        if args.variant == "wide128":
+            tactics.disable("routed_experts_wide256")
         ops.routed_experts(h, router, None, w_up, w_down, top, ids, weights, order, plan, act, y, gathered)
         used = int(torch.unique(ids).numel())
         moved = used * 3 * hidden * F * 2 + a * (hidden * 2 + F * 4 + hidden * 4)

@@ -362,6 +362,35 @@ def test_routed_experts_on_wide_tiles_agree_with_narrow_ones():
     assert float((y - y_narrow).abs().max()) <= 2e-2 * float(y_narrow.abs().max())
 
 
+def test_routed_experts_on_tiles_of_256_columns():
+    """Long lists (1,024 rows an expert and more) take tiles of 256 accumulator columns: the same step with those switched
+    off, and with all tcgen05 tiles switched off; sizes that are no multiple of any tile."""
+    ops = _ops()
+    from llm_b200.ops import tactics
+    hidden, F, E, top, n = 328, 136, 2, 1, 2300
+    gen = torch.Generator().manual_seed(5)
+    router = (3.0 * torch.randn((E, hidden), generator=gen) / hidden ** 0.5).to(DEV)
+    w_up = (torch.randn((E, 2 * F, hidden), generator=gen) / hidden ** 0.5).bfloat16().to(DEV)
+    w_down = (torch.randn((E, hidden, F), generator=gen) / F ** 0.5).bfloat16().to(DEV)
+    h = torch.randn((n, hidden), generator=gen).bfloat16().to(DEV)
+    ids, weights, y = _experts(ops.routed_experts, h, router, None, w_up, w_down, top)
+    results = []
+    for name in ("routed_experts_wide256", "routed_experts_wide"):
+        tactics.disable(name)
+        try:
+            results.append(_experts(ops.routed_experts, h, router, None, w_up, w_down, top))
+        finally:
+            tactics.enable(name)
+    torch.cuda.synchronize()
+    ops.check_device_status()
+    for other_ids, other_weights, other_y in results:
+        assert torch.equal(ids, other_ids) and torch.equal(weights, other_weights)
+        _close(y, other_y, torch.bfloat16, "rows")
+        assert float((y - other_y).abs().max()) <= 2e-2 * float(other_y.abs().max())
+    want = _experts(plain_ops.routed_experts, h[:64].contiguous(), router, None, w_up, w_down, top)[2]
+    _close(y[:64], want, torch.bfloat16, "rows against the plain statement")
+
+
 def test_routed_experts_choice_ties_and_batch_independence():
     """The bias alone decides when the router's matrix is zero; equal logits go to the lower index; a
     token's rows do not depend on what else is in the step (bit for bit in 32-bit)."""
