@@ -115,6 +115,25 @@ __device__ __forceinline__ void copy16(float* smem, const float* global) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(global));
 }
 
+// two 32-bit floats in one 64-bit register and the packed arithmetic on them (each half rounded as the scalar form)
+typedef unsigned long long pair_t;
+__device__ __forceinline__ pair_t pack2(float lo, float hi) {
+    pair_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(pair_t v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ pair_t fma2(pair_t a, pair_t b, pair_t c) {
+    pair_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ pair_t mul2(pair_t a, pair_t b) {
+    pair_t d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+
 constexpr int SCAN_THREADS = 128;
 constexpr int NC = 2;            // columns of S a thread holds
 constexpr int PAD = 4;           // floats between the slices of a staged q or k: a quarter warp's 16-byte loads fall into
@@ -160,6 +179,12 @@ delta_scan_kernel(const float* __restrict__ work, int work_ld, float* __restrict
             for (int c = 0; c < NC; ++c) S[c][e] = (d < D && col + c < V) ? S_global[(size_t)d * V + col + c] : 0.f;
         }
     }
+    // neighbouring elements of a column share a register pair: the sums and the update run as packed multiply-adds
+    pair_t S2[NC][DPT / 2];
+#pragma unroll
+    for (int c = 0; c < NC; ++c)
+#pragma unroll
+        for (int p2 = 0; p2 < DPT / 2; ++p2) S2[c][p2] = pack2(S[c][2 * p2], S[c][2 * p2 + 1]);
     // the padding of q and k (between slices and beyond D) stays zero in both buffers
     for (int i = threadIdx.x; i < 2 * buffer; i += SCAN_THREADS) stage[i] = 0.f;
     __syncthreads();
@@ -215,25 +240,32 @@ delta_scan_kernel(const float* __restrict__ work, int work_ld, float* __restrict
             const float* tok = buf + tt * per_token;
             const float4* q4 = reinterpret_cast<const float4*>(tok + slice * (DPT + PAD));
             const float4* k4 = reinterpret_cast<const float4*>(tok + Dq + slice * (DPT + PAD));
-            float k[DPT];
-            float sk[NC][4] = {}, sq[NC][4] = {};      // four chains a sum: a quarter of the latency of one
+            pair_t kp[DPT / 2];
+            pair_t sk[NC][2], sq[NC][2];               // two chains of pairs a sum: a quarter of the latency of one chain
+#pragma unroll
+            for (int c = 0; c < NC; ++c) { sk[c][0] = sk[c][1] = sq[c][0] = sq[c][1] = 0ull; }
 #pragma unroll
             for (int e = 0; e < DPT / 4; ++e) {
                 float4 kv = k4[e], qv = q4[e];
-                k[4 * e] = kv.x; k[4 * e + 1] = kv.y; k[4 * e + 2] = kv.z; k[4 * e + 3] = kv.w;
+                pair_t k01 = pack2(kv.x, kv.y), k23 = pack2(kv.z, kv.w), q01 = pack2(qv.x, qv.y), q23 = pack2(qv.z, qv.w);
+                kp[2 * e] = k01;
+                kp[2 * e + 1] = k23;
 #pragma unroll
                 for (int c = 0; c < NC; ++c) {
-                    sk[c][0] = fmaf(S[c][4 * e], kv.x, sk[c][0]); sq[c][0] = fmaf(S[c][4 * e], qv.x, sq[c][0]);
-                    sk[c][1] = fmaf(S[c][4 * e + 1], kv.y, sk[c][1]); sq[c][1] = fmaf(S[c][4 * e + 1], qv.y, sq[c][1]);
-                    sk[c][2] = fmaf(S[c][4 * e + 2], kv.z, sk[c][2]); sq[c][2] = fmaf(S[c][4 * e + 2], qv.z, sq[c][2]);
-                    sk[c][3] = fmaf(S[c][4 * e + 3], kv.w, sk[c][3]); sq[c][3] = fmaf(S[c][4 * e + 3], qv.w, sq[c][3]);
+                    sk[c][0] = fma2(S2[c][2 * e], k01, sk[c][0]); sq[c][0] = fma2(S2[c][2 * e], q01, sq[c][0]);
+                    sk[c][1] = fma2(S2[c][2 * e + 1], k23, sk[c][1]); sq[c][1] = fma2(S2[c][2 * e + 1], q23, sq[c][1]);
                 }
             }
             float tk[NC], tq[NC];
 #pragma unroll
             for (int c = 0; c < NC; ++c) {
-                tk[c] = (sk[c][0] + sk[c][1]) + (sk[c][2] + sk[c][3]);
-                tq[c] = (sq[c][0] + sq[c][1]) + (sq[c][2] + sq[c][3]);
+                float a0, a1, a2, a3;
+                unpack2(sk[c][0], a0, a1);
+                unpack2(sk[c][1], a2, a3);
+                tk[c] = (a0 + a1) + (a2 + a3);
+                unpack2(sq[c][0], a0, a1);
+                unpack2(sq[c][1], a2, a3);
+                tq[c] = (a0 + a1) + (a2 + a3);
             }
 #pragma unroll
             for (int offset = 16; offset >= pairs_per_warp; offset >>= 1) {
@@ -251,8 +283,9 @@ delta_scan_kernel(const float* __restrict__ work, int work_ld, float* __restrict
 #pragma unroll
             for (int c = 0; c < NC; ++c) {
                 o[c] = fmaf(u[c], kq, decay * tq[c]);
+                pair_t u2 = pack2(u[c], u[c]), d2 = pack2(decay, decay);
 #pragma unroll
-                for (int e = 0; e < DPT; ++e) S[c][e] = fmaf(k[e], u[c], decay * S[c][e]);
+                for (int p2 = 0; p2 < DPT / 2; ++p2) S2[c][p2] = fma2(kp[p2], u2, mul2(d2, S2[c][p2]));
             }
             if (slice == 0) {
                 float* dst = out + (size_t)(first + chunk * CHUNK + tt) * out_ld + a * V + col;
@@ -266,6 +299,10 @@ delta_scan_kernel(const float* __restrict__ work, int work_ld, float* __restrict
         }
         __syncthreads();
     }
+#pragma unroll
+    for (int c = 0; c < NC; ++c)
+#pragma unroll
+        for (int p2 = 0; p2 < DPT / 2; ++p2) unpack2(S2[c][p2], S[c][2 * p2], S[c][2 * p2 + 1]);
 #pragma unroll
     for (int e = 0; e < DPT; ++e) {
         int d = slice * DPT + e;
