@@ -1,7 +1,9 @@
-// The gated delta rule: a linear recurrence whose state is one matrix S [dim, vdim] per head,
-//     S <- g S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q
+// The gated delta rule: a linear recurrence whose state is one matrix M [dim, vdim] per head (S in the code),
+//     M_t = a_t M_{t-1} + k_t w_t^T,   w_t = b_t (v_t - a_t M_{t-1}^T k_t),   o_t = M_t^T q_t
+// (the state fades by a_t, then the row w_t is written under the key k_t: what the state already holds under that key is
+// taken off first; the read-out sees the token's own write),
 // behind short causal convolutions (with silu) on the q, k and v projections, unit-length q and k,
-// a sigmoid step size beta and a decay g = exp(rate * softplus(a + dt_bias)) per head, and in front of
+// a sigmoid step size b_t and a decay a_t = exp(rate * softplus(. + dt_bias)) per head, and in front of
 // a head-wise RMS norm with a silu gate.
 //
 // The projection row of a token is [q (G*D) | k (G*D) | v (H*V) | gate (H*V) | b (H) | a (H) | ...]
@@ -14,7 +16,7 @@
 // scan     one block per (columns of S, head, sequence) walks the sequence's tokens in order. Every
 //          column of S is a recurrence of its own: a thread holds 16 elements of two columns, DS threads
 //          a pair of columns; the two sums over dim use the state before the decay
-//          (S^T k after the decay is g times the sum before it, and o = g S^T q + u (k.q)), so both
+//          (o_t = a_t M_{t-1}^T q_t + w_t (k_t . q_t), and M_{t-1}^T k_t is summed before the decay), so both
 //          run as independent chains and are added over the DS threads by shuffles. Tokens are
 //          staged in shared memory eight at a time, the next eight requested under the current.
 // finish   o / sqrt(mean(o^2) + eps) * weight * silu(gate) per head, rounded to the run's dtype.

@@ -546,7 +546,7 @@ def delta_rule(proj, taps, state, tok_seq, cu_seqlens, slot_ids, rate, dt_bias, 
     q, k, v pass a causal convolution per channel (`taps` float32 [C, K], the last column the current
     token's) and silu; q and k become unit vectors per head (q also times D^-1/2); beta = sigmoid(b);
     decay = exp(rate * softplus(a + dt_bias)) (`rate` float32 [H], negative). Per head, token by token:
-    S <- decay S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q. Then o / sqrt(mean(o^2) + eps) *
+    M_t = a_t M_{t-1} + k_t w_t^T with w_t = b_t (v_t - a_t M_{t-1}^T k_t) (a_t the decay, b_t = beta); o_t = M_t^T q_t. Then o / sqrt(mean(o^2) + eps) *
     norm_weight * silu(gate) into `mixed` [T, H V] (run dtype). `state` float32 [slots, (K - 1) C + H D V]:
     the convolution's last inputs, then S; read and updated for the slots of the step. `work` float32
     [T, delta_rule_work_width], `o` float32 [T, H V]: scratch."""

@@ -12,18 +12,17 @@ from .projected import ProjectedMixer
 
 
 class DeltaRuleMixer(ProjectedMixer):
-    """Per head a state S [head_dim, value_dim], token by token
-        S <- g S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q
+    """Per head a state M [head_dim, value_dim], token by token
+        M_t = a_t M_{t-1} + k_t w_t^T,   w_t = b_t (v_t - a_t M_{t-1}^T k_t),   o_t = M_t^T q_t
     (the read-out sees the token's own write), with q, k (n_kv_heads heads, each serving a group of
     heads) and v behind a causal convolution per channel and silu, q and k of unit length (q also
-    times head_dim^-1/2), beta = sigmoid(W_b h), g = exp(-exp(A_log) softplus(W_a h + dt_bias)), and
-    o / rms(o) * weight * silu(W_g h) per head before the output product (Yang et al., "Gated Delta
-    Networks").
+    times head_dim^-1/2), b_t = sigmoid(W_b h), a_t = exp(-exp(A_log) softplus(W_a h + dt_bias)), and
+    o / rms(o) * weight * silu(W_g h) per head before the output product.
 
     One product [q; k; v; gate; b; a] (rows padded to a multiple of 8), then ops.delta_rule (the
     convolution with its state, unit norms, gates, the scan over each sequence's tokens, the heads'
     norm and gate), then the output product. Per sequence the cache holds one float32 row: the
-    convolution's last taps - 1 inputs [taps - 1, C], then S [heads, head_dim, value_dim]; zeroed
+    convolution's last taps - 1 inputs [taps - 1, C], then M [heads, head_dim, value_dim]; zeroed
     when a slot is taken. Everything behind the projection is 32-bit in every run."""
     libraries = ("elementwise", "gemm_simt", "gemm_skinny", "gemm_tc", "delta_rule")
 

@@ -37,7 +37,7 @@ def inverse_frequencies(head_dim: int, theta: float, scaling: dict | None) -> to
 
 
 def _ramp_scaled(freq, dims: int, theta: float, scaling: dict) -> torch.Tensor:
-    """Frequencies scaled by bands (Peng et al., "YaRN"): with dim(t) = dims ln(original / (2 pi t)) /
+    """Frequencies scaled by bands: with dim(t) = dims ln(original / (2 pi t)) /
     (2 ln theta) the pair index at which a wave makes t turns over the original context, pairs below
     lo = floor(dim(fast)) keep their frequency, pairs above hi = ceil(dim(slow)) are slowed by `factor`,
     and those between are blended linearly in the pair index."""

@@ -196,11 +196,11 @@ class GatedAttentionSpec:
 
 @dataclass(frozen=True)
 class DeltaRuleSpec:
-    """The gated delta rule (Yang et al., "Gated Delta Networks"): per head a state matrix S [head_dim,
-    value_dim] with S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q. q, k (n_kv_heads heads,
+    """The gated delta rule: per head a state matrix M [head_dim,
+    value_dim] with M_t = a_t M_{t-1} + k_t w_t^T with w_t = b_t (v_t - a_t M_{t-1}^T k_t); o_t = M_t^T q_t. q, k (n_kv_heads heads,
     shared by groups of query heads) and v (n_heads heads) pass a causal convolution of `conv_taps` taps
     per channel and silu; q and k are divided by sqrt(sum of squares + unit_eps), q also by
-    sqrt(head_dim); beta = sigmoid(W_b h); g = exp(-exp(A_log) softplus(W_a h + dt_bias)); every head's o
+    sqrt(head_dim); b_t = sigmoid(W_b h); a_t = exp(-exp(A_log) softplus(W_a h + dt_bias)); every head's o
     is divided by its root mean square (eps), multiplied by a weight of value_dim elements shared by
     the heads and by silu(W_g h)."""
     hidden: int
