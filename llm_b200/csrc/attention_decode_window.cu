@@ -88,7 +88,7 @@ attention_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                               __nv_bfloat16* __restrict__ out, int out_stride,
                               int n_heads, int n_kv_heads, float scale_log2, int window, int chunks,
                               const float* __restrict__ sinks, const __nv_bfloat16* __restrict__ gate,
-                              int gate_stride, float out_scale) {
+                              int gate_stride, float out_scale, float cap_log2) {
     constexpr int LDS = D + PAD;
     const bool values_are_keys = k_cache == v_cache;
     constexpr int PAGE_ELEMS = LLMB_PAGE * LDS;
@@ -216,7 +216,10 @@ attention_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         float local_max = -INFINITY;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            v[j] = (key[j] < len && key[j] >= oldest) ? v[j] * scale_log2 : -INFINITY;
+            float scaled = v[j] * scale_log2;
+            // a soft cap c bounds the scaled score, c tanh(s / c); in base-2 units both carry the factor log2(e)
+            if (cap_log2 > 0.f) scaled = cap_log2 * tanhf(scaled / cap_log2);
+            v[j] = (key[j] < len && key[j] >= oldest) ? scaled : -INFINITY;
             local_max = fmaxf(local_max, v[j]);
         }
         local_max = fmaxf(local_max, __shfl_xor_sync(0xffffffffu, local_max, 1));
@@ -315,7 +318,7 @@ static int launch(const void* q, int q_stride, const void* k_cache, const void* 
                   const int* block_table, int table_stride, int ring_pages, const int* seq_lens,
                   const int* seq_order, void* out, int out_stride, float* scratch, int n_seqs, int n_heads,
                   int n_kv_heads, float scale, int window, const float* sinks, const void* gate, int gate_stride,
-                  float out_scale, int n_splits, cudaStream_t stream) {
+                  float out_scale, float softcap, int n_splits, cudaStream_t stream) {
     constexpr int LDS = D + PAD;
     constexpr int STAGES = stages_for<D>();
     size_t stage_bytes = (size_t)STAGES * pages_per_stage<D>() * 2 * LLMB_PAGE * LDS * sizeof(__nv_bfloat16);
@@ -335,7 +338,8 @@ static int launch(const void* q, int q_stride, const void* k_cache, const void* 
                  (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache,
                  (const __nv_bfloat16*)v_cache, block_table, table_stride, ring_pages, seq_lens, seq_order,
                  part_acc, part_stats, (__nv_bfloat16*)out, out_stride, n_heads, n_kv_heads, scale * 1.4426950408889634f,
-                 window, chunks, sinks, (const __nv_bfloat16*)gate, gate_stride, out_scale);
+                 window, chunks, sinks, (const __nv_bfloat16*)gate, gate_stride, out_scale,
+                 softcap > 0.f ? softcap * 1.4426950408889634f : 0.f);
     int code = check_launch("attention_decode_window_split");
     if (code || n_splits == 1) return code;
     llmb::launch(attention_decode_combine_kernel<D>, dim3(n_heads, n_seqs), D >= 128 ? 128 : 64, 0, stream, true,
@@ -370,7 +374,7 @@ LLMB_EXPORT int llmb_attention_decode_window(const void* q, int q_stride, const 
                                       int out_stride, float* scratch, long long scratch_floats, int n_seqs,
                                       int n_heads, int n_kv_heads, int head_dim, float scale,
                                       int window, const float* sinks, const void* gate, int gate_stride,
-                                      float out_scale, int n_splits, cudaStream_t stream) {
+                                      float out_scale, float softcap, int n_splits, cudaStream_t stream) {
     if (n_seqs == 0) return LLMB_OK;
     int code = llmb_attention_decode_window_supports(n_heads, n_kv_heads, head_dim, window);
     if (code) return code;
@@ -383,7 +387,7 @@ LLMB_EXPORT int llmb_attention_decode_window(const void* q, int q_stride, const 
                  "attention_decode_window: scratch too small");
 #define ARGS q, q_stride, k_cache, v_cache, block_table, table_stride, ring_pages, seq_lens, seq_order, out, \
              out_stride, scratch, n_seqs, n_heads, n_kv_heads, scale, window, sinks, gate, gate_stride, out_scale, \
-             n_splits, stream
+             softcap, n_splits, stream
     switch (head_dim) {
         case 32: return launch<32>(ARGS);
         case 64: return launch<64>(ARGS);

@@ -33,6 +33,9 @@ constexpr int WARPS = 4;
 // (e^sink is one more term of the head's softmax denominator: it has no key and no value and is not
 // scaled), `gate` [T, heads] (the head's result is multiplied by sigmoid(gate)), `out_scale`. When the
 // value cache IS the key cache (a mixer whose cached rows serve as both), a row is loaded once.
+// `softcap` > 0 bounds a score before the softmax: s <- softcap * tanh(s / softcap), after the scale.
+// Values may be wider or narrower than keys (`value_dim`; the value cache then has rows of that size and
+// the result rows hold n_heads * value_dim elements).
 template <typename T, int AHEAD, int MAX_PER_LANE>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_generic_kernel(const T* __restrict__ q, int q_stride, const T* __restrict__ k_cache,
@@ -41,7 +44,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, const T* __restr
                          const int* __restrict__ tok_seq, T* __restrict__ out, int out_stride,
                          int n_heads, int n_kv_heads, int head_dim, float scale, int window,
                          const float* __restrict__ sinks, const T* __restrict__ gate, int gate_stride,
-                         float out_scale) {
+                         float out_scale, float softcap, int value_dim) {
     int t = blockIdx.x, head = blockIdx.y;
     const bool values_are_keys = k_cache == v_cache;
     int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -70,13 +73,14 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, const T* __restr
             int j = j0 + u * WARPS;
             bool visible = j <= pos;
             int page = visible ? pages[(j / LLMB_PAGE) % ring_pages] : 0;
-            size_t offset = (((size_t)page * n_kv_heads + kv_head) * LLMB_PAGE + (j % LLMB_PAGE)) * head_dim;
+            size_t row = ((size_t)page * n_kv_heads + kv_head) * LLMB_PAGE + (j % LLMB_PAGE);
+            size_t offset = row * head_dim, v_offset = row * value_dim;
 #pragma unroll
             for (int i = 0; i < MAX_PER_LANE; ++i) {
                 int d = lane + 32 * i;
                 bool live = visible && d < head_dim;
                 kv[u][i] = live ? to_float(k_cache[offset + d]) : 0.f;
-                vv[u][i] = values_are_keys ? kv[u][i] : (live ? to_float(v_cache[offset + d]) : 0.f);
+                vv[u][i] = values_are_keys ? kv[u][i] : (visible && d < value_dim ? to_float(v_cache[v_offset + d]) : 0.f);
             }
         }
 #pragma unroll
@@ -89,6 +93,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, const T* __restr
                 if (d < head_dim) dot = fmaf(qv[i], kv[u][i], dot);
             }
             float score = warp_sum(dot) * scale;
+            if (softcap > 0.f) score = softcap * tanhf(score / softcap);
             float new_max = fmaxf(running_max, score);
             float rescale = expf(running_max - new_max);    // exp(-inf) = 0 on the first key
             float p = expf(score - new_max);
@@ -96,7 +101,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, const T* __restr
 #pragma unroll
             for (int i = 0; i < MAX_PER_LANE; ++i) {
                 int d = lane + 32 * i;
-                if (d < head_dim) acc[i] = fmaf(p, vv[u][i], acc[i] * rescale);
+                if (d < value_dim) acc[i] = fmaf(p, vv[u][i], acc[i] * rescale);
             }
             running_max = new_max;
         }
@@ -122,11 +127,11 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, const T* __restr
         }
         float factor = out_scale;
         if (gate) factor *= 1.0f / (1.0f + expf(-to_float(gate[(size_t)t * gate_stride + head])));
-        T* o = out + (size_t)t * out_stride + (size_t)head * head_dim;
+        T* o = out + (size_t)t * out_stride + (size_t)head * value_dim;
 #pragma unroll
         for (int i = 0; i < MAX_PER_LANE; ++i) {
             int d = lane + 32 * i;
-            if (d < head_dim) {
+            if (d < value_dim) {
                 float v = 0.f;
 #pragma unroll
                 for (int w = 0; w < WARPS; ++w) v += part_acc[w][d] * weight[w];
@@ -142,21 +147,24 @@ LLMB_EXPORT int llmb_attention_generic(const void* q, int q_stride, const void* 
                                        const int* tok_seq, void* out, int out_stride, int dtype,
                                        int n_tokens, int n_heads, int n_kv_heads, int head_dim,
                                        float scale, int window, const float* sinks, const void* gate,
-                                       int gate_stride, float out_scale, cudaStream_t stream) {
+                                       int gate_stride, float out_scale, float softcap, int value_dim,
+                                       cudaStream_t stream) {
     if (n_tokens == 0) return LLMB_OK;
-    LLMB_REQUIRE(head_dim > 0 && head_dim <= GENERIC_MAX_HEAD_DIM,
-                 "attention_generic: head_dim %d exceeds %d", head_dim, GENERIC_MAX_HEAD_DIM);
+    if (value_dim <= 0) value_dim = head_dim;
+    LLMB_REQUIRE(head_dim > 0 && head_dim <= GENERIC_MAX_HEAD_DIM && value_dim <= GENERIC_MAX_HEAD_DIM,
+                 "attention_generic: head_dim %d or value_dim %d exceeds %d", head_dim, value_dim, GENERIC_MAX_HEAD_DIM);
+    LLMB_REQUIRE(k_cache != v_cache || value_dim == head_dim, "attention_generic: values that are the keys have their size");
     LLMB_REQUIRE(n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0,
                  "attention_generic: %d heads are no multiple of %d kv heads", n_heads, n_kv_heads);
     LLMB_REQUIRE(n_heads <= 65535 && ring_pages > 0 && window >= 0, "attention_generic: bad sizes");
     dim3 grid(n_tokens, n_heads);
     bool few = (long long)n_tokens * n_heads < 4096;       // the result is the same either way
-    bool wide = head_dim > LLMB_MAX_HEAD_DIM;              // twice the registers a lane: only where the head needs them
+    bool wide = head_dim > LLMB_MAX_HEAD_DIM || value_dim > LLMB_MAX_HEAD_DIM;              // twice the registers a lane: only where the head needs them
 #define LLMB_GENERIC_AS(T, AHEAD, PER)                                                                  \
     attention_generic_kernel<T, AHEAD, PER><<<grid, WARPS * 32, 0, stream>>>(                            \
         (const T*)q, q_stride, (const T*)k_cache, (const T*)v_cache, block_table, table_stride,         \
         ring_pages, tok_pos, tok_seq, (T*)out, out_stride, n_heads, n_kv_heads, head_dim, scale, window, \
-        sinks, (const T*)gate, gate_stride, out_scale)
+        sinks, (const T*)gate, gate_stride, out_scale, softcap, value_dim)
 #define LLMB_GENERIC(T, AHEAD)                                                                          \
     do {                                                                                                \
         if (wide) LLMB_GENERIC_AS(T, 1, GENERIC_MAX_HEAD_DIM / 32);                                      \

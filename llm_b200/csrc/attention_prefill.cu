@@ -60,7 +60,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                          const int* __restrict__ cu_seqlens, const int* __restrict__ seq_lens,
                          __nv_bfloat16* __restrict__ out, int out_stride, int n_heads,
                          int n_kv_heads, float scale_log2, int window, const float* __restrict__ sinks,
-                         const __nv_bfloat16* __restrict__ gate, int gate_stride, float out_scale) {
+                         const __nv_bfloat16* __restrict__ gate, int gate_stride, float out_scale,
+                         float cap_raw) {
     constexpr int LDS = D + PAD;
     const bool values_are_keys = k_cache == v_cache;
     constexpr int PAGE_ELEMS = LLMB_PAGE * LDS;
@@ -155,6 +156,14 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
             }
         }
         // s[nb][0..1]: row0, keys key0 + nb * 8 + 2t, +1; s[nb][2..3]: row1, the same keys.
+        // A soft cap bounds the scaled score: c tanh(s * scale / c); cap_raw = c / scale keeps it in raw units.
+        if (cap_raw > 0.f) {
+            float inv_cap = 1.0f / cap_raw;
+#pragma unroll
+            for (int nb = 0; nb < 8; ++nb)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) s[nb][i] = cap_raw * tanhf(s[nb][i] * inv_cap);
+        }
         // Maxima are kept on the raw scores (the scale is positive); the scale and log2(e) are
         // applied inside the exponent with one fused multiply-add per score.
         bool diagonal = key0 + LLMB_PAGE - 1 > start + tile * BQ + warp * 16;   // some key may be hidden
@@ -263,7 +272,7 @@ static int launch(const void* q, int q_stride, const void* k_cache, const void* 
                   const int* block_table, int table_stride, int ring_pages, const int* cu_seqlens,
                   const int* seq_lens, void* out, int out_stride, int n_seqs, int max_new, int n_heads,
                   int n_kv_heads, float scale, int window, const float* sinks, const void* gate, int gate_stride,
-                  float out_scale, cudaStream_t stream) {
+                  float out_scale, float softcap, cudaStream_t stream) {
     constexpr int LDS = D + PAD;
     size_t smem = (size_t)STAGES * 2 * LLMB_PAGE * LDS * sizeof(__nv_bfloat16);
     static bool configured = false;
@@ -277,7 +286,7 @@ static int launch(const void* q, int q_stride, const void* k_cache, const void* 
         (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
         block_table, table_stride, ring_pages, cu_seqlens, seq_lens, (__nv_bfloat16*)out, out_stride,
         n_heads, n_kv_heads, scale * 1.4426950408889634f, window, sinks, (const __nv_bfloat16*)gate, gate_stride,
-        out_scale);
+        out_scale, softcap > 0.f ? softcap / scale : 0.f);
     return check_launch("attention_prefill");
 }
 
@@ -299,8 +308,9 @@ LLMB_EXPORT int llmb_attention_prefill(const void* q, int q_stride, const void* 
                                        void* out, int out_stride, int n_seqs, int max_new,
                                        int n_heads, int n_kv_heads, int head_dim, float scale,
                                        int window, const float* sinks, const void* gate, int gate_stride,
-                                       float out_scale, cudaStream_t stream) {
+                                       float out_scale, float softcap, cudaStream_t stream) {
     if (n_seqs == 0 || max_new == 0) return LLMB_OK;
+    LLMB_REQUIRE(softcap <= 0.f || scale > 0.f, "attention_prefill: a soft cap needs a positive scale");
     int code = llmb_attention_prefill_supports(n_heads, n_kv_heads, head_dim, window);
     if (code) return code;
     LLMB_REQUIRE(n_seqs <= 65535 && max_new / BQ < 65535 && ring_pages > 0, "attention_prefill: bad sizes");
@@ -309,7 +319,7 @@ LLMB_EXPORT int llmb_attention_prefill(const void* q, int q_stride, const void* 
                  "attention_prefill: q and out must be 4-byte aligned with even row strides");
 #define ARGS q, q_stride, k_cache, v_cache, block_table, table_stride, ring_pages, cu_seqlens, seq_lens, \
              out, out_stride, n_seqs, max_new, n_heads, n_kv_heads, scale, window, sinks, gate, gate_stride, \
-             out_scale, stream
+             out_scale, softcap, stream
     switch (head_dim) {
         case 32: return launch<32>(ARGS);
         case 64: return launch<64>(ARGS);

@@ -9,6 +9,13 @@
 // float64 by the position encoding), and only the stores round to the run's dtype. Without a gain a
 // segment is not normed; without a table nothing rotates; with v_width == 0 there are no values (a mixer
 // whose cached row serves as key and value).
+//
+// With norm_unit > 0 the norms run over units of that many columns instead (a head each: every unit of
+// the queries and of the keys is divided by its own root mean square, and the gain has norm_unit elements
+// that all units share); a warp takes a unit, its lanes the unit's elements in strides of 32.
+// With mix_cache the values are blended before they are cached: v <- (1 - mix) v + mix * first, where
+// `first` is the row that another layer's value cache (mix_cache, with its own page table and ring) holds
+// for the same token, key/value head and element; that layer must have written the step's tokens before.
 #include "common.cuh"
 
 using namespace llmb;
@@ -37,7 +44,8 @@ norm_rope_cache_write_kernel(const T* __restrict__ u, int u_stride, int q_width,
                              const int* __restrict__ tok_pos, const int* __restrict__ tok_seq, T* __restrict__ q_out,
                              int q_out_stride, const int* __restrict__ block_table, int table_stride, int ring_pages,
                              T* __restrict__ k_cache, int k_heads, T* __restrict__ v_cache, int v_heads,
-                             int write_cache, int v_source) {
+                             int write_cache, int v_source, int norm_unit, const T* __restrict__ mix_cache,
+                             const int* __restrict__ mix_table, int mix_table_stride, int mix_ring, float mix) {
     extern __shared__ float row[];         // [q_width + k_width]
     __shared__ float scratch[THREADS / 32];
     griddep_launch();
@@ -52,14 +60,28 @@ norm_rope_cache_write_kernel(const T* __restrict__ u, int u_stride, int q_width,
         if (e < q_width) sq_q = fmaf(v, v, sq_q);
         else sq_k = fmaf(v, v, sq_k);
     }
-    float q_scale = 1.f, k_scale = 1.f;
-    if (q_gain) q_scale = 1.0f / sqrtf(block_sum(sq_q, scratch) / (float)q_width + eps);
-    if (k_gain && write_cache) k_scale = 1.0f / sqrtf(block_sum(sq_k, scratch) / (float)k_width + eps);
-    __syncthreads();
-    for (int e = threadIdx.x; e < qk; e += THREADS) {
-        bool is_q = e < q_width;
-        const float* gain = is_q ? q_gain : k_gain;
-        if (gain) row[e] = row[e] * (is_q ? q_scale : k_scale) * gain[is_q ? e : e - q_width];
+    if (norm_unit > 0) {
+        __syncthreads();
+        int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        for (int unit = warp; unit < qk / norm_unit; unit += THREADS / 32) {
+            float* x = row + unit * norm_unit;
+            const float* gain = unit * norm_unit < q_width ? q_gain : k_gain;
+            if (!gain) continue;
+            float sq = 0.f;
+            for (int d = lane; d < norm_unit; d += 32) sq = fmaf(x[d], x[d], sq);
+            float factor = 1.0f / sqrtf(warp_sum(sq) / (float)norm_unit + eps);
+            for (int d = lane; d < norm_unit; d += 32) x[d] = x[d] * factor * gain[d];
+        }
+    } else {
+        float q_scale = 1.f, k_scale = 1.f;
+        if (q_gain) q_scale = 1.0f / sqrtf(block_sum(sq_q, scratch) / (float)q_width + eps);
+        if (k_gain && write_cache) k_scale = 1.0f / sqrtf(block_sum(sq_k, scratch) / (float)k_width + eps);
+        __syncthreads();
+        for (int e = threadIdx.x; e < qk; e += THREADS) {
+            bool is_q = e < q_width;
+            const float* gain = is_q ? q_gain : k_gain;
+            if (gain) row[e] = row[e] * (is_q ? q_scale : k_scale) * gain[is_q ? e : e - q_width];
+        }
     }
     __syncthreads();
     int pos = tok_pos[t];
@@ -94,9 +116,16 @@ norm_rope_cache_write_kernel(const T* __restrict__ u, int u_stride, int q_width,
     if (write_cache && v_width > 0) {
         int v_dim = v_width / v_heads;
         const T* values = in + v_source;       // as projected: a source inside the key columns gives the keys before rotation
+        size_t mix_page = 0;
+        if (mix_cache) mix_page = (size_t)mix_table[(size_t)tok_seq[t] * mix_table_stride + (pos / LLMB_PAGE) % mix_ring];
         for (int e = threadIdx.x; e < v_width; e += THREADS) {
             int head = e / v_dim, d = e % v_dim;
-            v_cache[((page * v_heads + head) * LLMB_PAGE + slot_row) * v_dim + d] = values[e];
+            T value = values[e];
+            if (mix_cache) {
+                float first = to_float(mix_cache[((mix_page * v_heads + head) * LLMB_PAGE + slot_row) * v_dim + d]);
+                value = from_float<T>((1.0f - mix) * to_float(value) + mix * first);
+            }
+            v_cache[((page * v_heads + head) * LLMB_PAGE + slot_row) * v_dim + d] = value;
         }
     }
 }
@@ -109,8 +138,9 @@ LLMB_EXPORT int llmb_norm_rope_cache_write(const void* u, int u_stride, int dtyp
                                            int n_rot, int rot_unit, int interleaved, const int* tok_pos,
                                            const int* tok_seq, void* q_out, int q_out_stride, const int* block_table,
                                            int table_stride, int ring_pages, void* k_cache, int k_heads, void* v_cache,
-                                           int v_heads, int write_cache, int v_source, int n_tokens,
-                                           cudaStream_t stream) {
+                                           int v_heads, int write_cache, int v_source, int norm_unit,
+                                           const void* mix_cache, const int* mix_table, int mix_table_stride,
+                                           int mix_ring, float mix, int n_tokens, cudaStream_t stream) {
     if (n_tokens == 0) return LLMB_OK;
     LLMB_REQUIRE(q_width > 0 && k_width > 0 && v_width >= 0 && k_heads > 0 && k_width % k_heads == 0,
                  "norm_rope_cache_write: bad widths %d / %d / %d with %d key heads", q_width, k_width, v_width, k_heads);
@@ -121,6 +151,10 @@ LLMB_EXPORT int llmb_norm_rope_cache_write(const void* u, int u_stride, int dtyp
                  "norm_rope_cache_write: %d rotated elements do not fit units of %d", n_rot, rot_unit);
     LLMB_REQUIRE(ring_pages > 0, "norm_rope_cache_write: no pages");
     LLMB_REQUIRE(v_source >= 0, "norm_rope_cache_write: the values start at column %d", v_source);
+    LLMB_REQUIRE(norm_unit >= 0 && (norm_unit == 0 || (q_width % norm_unit == 0 && k_width % norm_unit == 0)),
+                 "norm_rope_cache_write: units of %d columns do not divide %d and %d", norm_unit, q_width, k_width);
+    LLMB_REQUIRE(!mix_cache || (mix_table && mix_ring > 0 && v_width > 0 && mix_cache != v_cache),
+                 "norm_rope_cache_write: values are blended with another layer's cache, which needs its page table");
     size_t smem = sizeof(float) * (size_t)(q_width + k_width);
     LLMB_REQUIRE(smem <= 200 * 1024, "norm_rope_cache_write: a row of %d + %d values does not fit in shared memory",
                  q_width, k_width);
@@ -133,7 +167,8 @@ LLMB_EXPORT int llmb_norm_rope_cache_write(const void* u, int u_stride, int dtyp
                                (const T*)u, u_stride, q_width, k_width, v_width, q_gain, k_gain, eps, rope_table,   \
                                rope_table ? n_rot : 0, rot_unit > 0 ? rot_unit : 1, interleaved, tok_pos, tok_seq,   \
                                (T*)q_out, q_out_stride, block_table, table_stride, ring_pages, (T*)k_cache, k_heads, \
-                               (T*)v_cache, v_heads, write_cache, v_source));                                        \
+                               (T*)v_cache, v_heads, write_cache, v_source, norm_unit, (const T*)mix_cache,          \
+                               mix_table, mix_table_stride, mix_ring, mix));                                        \
     } while (0)
     if (dtype == LLMB_DTYPE_F32) LLMB_NORM_ROPE(float);
     else if (dtype == LLMB_DTYPE_BF16) LLMB_NORM_ROPE(__nv_bfloat16);

@@ -6,6 +6,12 @@
 //          expert at a time), or, for steps of 512 tokens and more, four warps per four tokens (a weight row is
 //          fetched once for the four). An
 //          assignment is a pair (token, k): index t * top + k.
+//          `scoring` 1 instead: scores s = softmax over ALL router outputs; the `top` largest of s + correction are
+//          chosen (the correction takes part in the choice only), weights s / (sum of the chosen s + 1e-20). The
+//          router may have more outputs than there are experts: the last ones are pass-through experts without
+//          matrices whose result is the token's own row h (times the weight); a small kernel writes those rows,
+//          the plan and the products see only the assignments of experts that have matrices.
+//          `weight_scale` multiplies every weight (a constant in front of the whole feed-forward).
 // plan     counts the assignments of every expert, lists them grouped by expert (inside an expert in rising
 //          order, so the plan is a function of the routing alone) and cuts every expert's list into tiles of 32
 //          (or, for the tcgen05 products, 128) rows: (expert, first row, rows) per tile. Nothing of this reaches
@@ -53,7 +59,8 @@ __device__ __forceinline__ void load4(const __nv_bfloat16* p, float (&x)[4]) {
 template <typename T, int TOK>
 __global__ void __launch_bounds__(512)
 router_kernel(const T* __restrict__ h, int ld, const float* __restrict__ w, const float* __restrict__ bias,
-              int hidden, int E, int top, int* __restrict__ ids, float* __restrict__ weights, int n_tokens, int vectors) {
+              int hidden, int E, int top, int* __restrict__ ids, float* __restrict__ weights, int n_tokens, int vectors,
+              int scoring, const float* __restrict__ correction, float weight_scale) {
     extern __shared__ float logits[];      // [TOK][E]
     griddep_launch();
     griddep_wait();
@@ -103,6 +110,29 @@ router_kernel(const T* __restrict__ h, int ld, const float* __restrict__ w, cons
     size_t t = t0 + threadIdx.x;
     float* mine = logits + threadIdx.x * E;
     float chosen[MAX_TOP];
+    if (scoring == 1) {
+        // softmax over every output (terms in index order), the choice by score + correction, the weights by score
+        float largest = -INFINITY, total = 0.f;
+        for (int e = 0; e < E; ++e) largest = fmaxf(largest, mine[e]);
+        for (int e = 0; e < E; ++e) total += expf(mine[e] - largest);
+        for (int e = 0; e < E; ++e) mine[e] = expf(mine[e] - largest) / total;      // scores: never negative
+        float sum = 0.f;
+        for (int k = 0; k < top; ++k) {
+            int best = 0;
+            float value = -INFINITY;
+            for (int e = 0; e < E; ++e) {
+                if (mine[e] < 0.f) continue;                  // taken already
+                float c = mine[e] + (correction ? correction[e] : 0.f);
+                if (c > value) { value = c; best = e; }
+            }
+            chosen[k] = mine[best];
+            sum += chosen[k];
+            ids[t * top + k] = best;
+            mine[best] = -1.f;
+        }
+        for (int k = 0; k < top; ++k) weights[t * top + k] = chosen[k] / (sum + 1e-20f) * weight_scale;
+        return;
+    }
     for (int k = 0; k < top; ++k) {
         int best = 0;
         float value = -INFINITY;
@@ -114,7 +144,22 @@ router_kernel(const T* __restrict__ h, int ld, const float* __restrict__ w, cons
     }
     float total = 0.f, largest = chosen[0];
     for (int k = 0; k < top; ++k) { chosen[k] = expf(chosen[k] - largest); total += chosen[k]; }
-    for (int k = 0; k < top; ++k) weights[t * top + k] = chosen[k] / total;
+    for (int k = 0; k < top; ++k) weights[t * top + k] = chosen[k] / total * weight_scale;
+}
+
+// y[a, :] = weights[a] * h[a / top, :] for the assignments a of pass-through experts (ids[a] >= E): 32-bit rows at
+// the assignment's own index, like the rows the down product leaves.
+template <typename T>
+__global__ void __launch_bounds__(256)
+pass_through_kernel(const T* __restrict__ h, int ld, int top, const int* __restrict__ ids,
+                    const float* __restrict__ weights, int E, int hidden, float* __restrict__ y) {
+    griddep_launch();
+    griddep_wait();
+    int a = blockIdx.x;
+    if (ids[a] < E) return;
+    float wgt = weights[a];
+    const T* row = h + (size_t)(a / top) * ld;
+    for (int c = threadIdx.x; c < hidden; c += 256) y[(size_t)a * hidden + c] = wgt * to_float(row[c]);
 }
 
 // plan: [0, E] offsets | [E + 1] tile count | then three arrays of max_tiles: expert, first row, rows.
@@ -136,7 +181,8 @@ plan_kernel(const int* __restrict__ ids, int n_assign, int E, int* __restrict__ 
     constexpr int n_warps = PLAN_THREADS / 32;
     for (int e = threadIdx.x; e < E; e += PLAN_THREADS) counts[e] = 0;
     __syncthreads();
-    for (int i = threadIdx.x; i < n_assign; i += PLAN_THREADS) atomicAdd(&counts[ids[i]], 1);
+    for (int i = threadIdx.x; i < n_assign; i += PLAN_THREADS)
+        if (ids[i] < E) atomicAdd(&counts[ids[i]], 1);          // (an id beyond E is a pass-through expert: no rows)
     __syncthreads();
     if (threadIdx.x == 0) {
         int at = 0, tiles = 0;
@@ -408,12 +454,12 @@ __host__ __device__ constexpr size_t smem_of(int gn) { return 1024 + (size_t)sta
 
 // Xs[s, :] = h[sorted[s] / top, :]: the rows of h in the order of the plan (16 bytes a thread a time).
 __global__ void __launch_bounds__(256)
-gather_rows_kernel(const __nv_bfloat16* __restrict__ h, int ld, int top, const int* __restrict__ sorted, int n_assign,
-                   int hidden, __nv_bfloat16* __restrict__ out) {
+gather_rows_kernel(const __nv_bfloat16* __restrict__ h, int ld, int top, const int* __restrict__ sorted,
+                   const int* __restrict__ plan, int E, int hidden, __nv_bfloat16* __restrict__ out) {
     griddep_launch();
     griddep_wait();
     int per_row = hidden / 8;
-    long long total = (long long)n_assign * per_row;
+    long long total = (long long)plan[E] * per_row;            // the listed assignments (those of experts with matrices)
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
         int s = (int)(i / per_row), c = (int)(i % per_row);
         const uint4* src = reinterpret_cast<const uint4*>(h + (long long)(sorted[s] / top) * ld) + c;
@@ -618,10 +664,13 @@ LLMB_EXPORT long long llmb_routed_experts_plan_ints(int n_tokens, int top, int E
 LLMB_EXPORT int llmb_routed_experts(const void* h, int ld, int dtype, const float* router, const float* router_bias,
                                     const void* w_up, const void* w_down, int* ids, float* weights, int* sorted,
                                     int* plan, void* act, float* y, void* gathered, int n_tokens, int hidden, int F,
-                                    int E, int top, int tensor_cores, cudaStream_t stream) {
+                                    int E, int top, int tensor_cores, int scoring, const float* correction,
+                                    int pass_through, float weight_scale, cudaStream_t stream) {
     if (n_tokens == 0) return LLMB_OK;
-    LLMB_REQUIRE(hidden > 0 && F > 0 && E > 0 && top > 0 && top <= E && top <= MAX_TOP,
-                 "routed_experts: %d of %d experts (at most %d are chosen)", top, E, MAX_TOP);
+    LLMB_REQUIRE(hidden > 0 && F > 0 && E > 0 && top > 0 && pass_through >= 0 && top <= E + pass_through && top <= MAX_TOP,
+                 "routed_experts: %d of %d experts (at most %d are chosen)", top, E + pass_through, MAX_TOP);
+    LLMB_REQUIRE(scoring == 0 || scoring == 1, "routed_experts: scoring %d (0: softmax over the chosen, 1: over all)", scoring);
+    int R = E + pass_through;                                  // outputs of the router
     LLMB_REQUIRE(E <= 2048, "routed_experts: %d experts (up to 2048 are built)", E);
     int n_assign = n_tokens * top;
     int max_tiles = (n_assign + TILE_M - 1) / TILE_M + E;
@@ -637,13 +686,16 @@ LLMB_EXPORT int llmb_routed_experts(const void* h, int ld, int dtype, const floa
 #define LLMB_EXPERTS(T)                                                                                            \
     do {                                                                                                           \
         if (n_tokens >= 512)                                                                                       \
-            LLMB_CUDA(llmb::launch(router_kernel<T, 4>, dim3((n_tokens + 3) / 4), dim3(128), sizeof(float) * 4 * E, \
-                                   stream, true, (const T*)h, ld, router, router_bias, hidden, E, top, ids,       \
-                                   weights, n_tokens, router_vectors));                                            \
+            LLMB_CUDA(llmb::launch(router_kernel<T, 4>, dim3((n_tokens + 3) / 4), dim3(128), sizeof(float) * 4 * R, \
+                                   stream, true, (const T*)h, ld, router, router_bias, hidden, R, top, ids,       \
+                                   weights, n_tokens, router_vectors, scoring, correction, weight_scale));        \
         else                                                                                                       \
-            LLMB_CUDA(llmb::launch(router_kernel<T, 1>, dim3(n_tokens), dim3(512), sizeof(float) * E, stream,     \
-                                   true, (const T*)h, ld, router, router_bias, hidden, E, top, ids, weights,       \
-                                   n_tokens, router_vectors));                                                     \
+            LLMB_CUDA(llmb::launch(router_kernel<T, 1>, dim3(n_tokens), dim3(512), sizeof(float) * R, stream,     \
+                                   true, (const T*)h, ld, router, router_bias, hidden, R, top, ids, weights,       \
+                                   n_tokens, router_vectors, scoring, correction, weight_scale));                  \
+        if (pass_through > 0)                                                                                      \
+            LLMB_CUDA(llmb::launch(pass_through_kernel<T>, dim3(n_assign), dim3(256), 0, stream, true, (const T*)h, \
+                                   ld, top, (const int*)ids, (const float*)weights, E, hidden, y));                \
         LLMB_CUDA(llmb::launch(plan_kernel, dim3(E < 64 ? E : 64), dim3(PLAN_THREADS),                             \
                                sizeof(int) * (3 * E + 2 + 32), stream, true, (const int*)ids, n_assign, E, sorted, \
                                plan, max_tiles, tile_m));                                                          \
@@ -683,7 +735,7 @@ LLMB_EXPORT int llmb_routed_experts(const void* h, int ld, int dtype, const floa
         long long vectors = (long long)n_assign * (hidden / 8);
         int gather_blocks = (int)((vectors + 255) / 256 < 148 * 8 ? (vectors + 255) / 256 : 148 * 8);
         LLMB_CUDA(llmb::launch(gather_rows_kernel, dim3(gather_blocks), dim3(256), 0, stream, true, (const B*)h, ld, top,
-                               (const int*)sorted, n_assign, hidden, (B*)gathered));
+                               (const int*)sorted, (const int*)plan, E, hidden, (B*)gathered));
         auto up = wide256 ? expert_product_wide_kernel<true, 256> : expert_product_wide_kernel<true, 128>;
         auto down = wide256 ? expert_product_wide_kernel<false, 256> : expert_product_wide_kernel<false, 128>;
         LLMB_CUDA(llmb::launch(up, dim3((F + GN / 2 - 1) / (GN / 2), tiles), dim3(G_THREADS), smem, stream, true, map_x, map_up,

@@ -416,7 +416,8 @@ def _check_rows(t, n: int, width: int, dtype, what: str):
 
 def norm_rope_cache_write(u, q_width, k_width, v_width, q_gain, k_gain, eps, rope_table, rot_unit, interleaved,
                           tok_pos, tok_seq, q_out, block_table, ring_pages, k_cache, v_cache, write_cache=True,
-                          value_source=None):
+                          value_source=None, norm_unit: int = 0, mix_cache=None, mix_table=None, mix_ring: int = 0,
+                          mix: float = 0.0):
     """What lies between a projection and the attention of a mixer that norms whole projections:
     the first q_width columns of `u` are the queries, the next k_width the keys, the next v_width
     the values (u may have more columns). With `q_gain` (float32 [q_width]) the queries of a token
@@ -426,8 +427,13 @@ def norm_rope_cache_write(u, q_width, k_width, v_width, q_gain, k_gain, eps, rop
     keys into k_cache [pages, Hk, 64, Dk] (Hk * Dk = k_width), values (v_width > 0) into v_cache
     [pages, Hv, 64, Dv]. Sums, the norm's factor and angles are 32-bit. `value_source` (a column of u;
     default q_width + k_width): where a token's values start; q_width makes the values the keys as
-    projected, before norm and rotation (a mixer without a value projection)."""
-    _require_cuda(u, q_gain, k_gain, rope_table, tok_pos, tok_seq, q_out, block_table, k_cache, v_cache)
+    projected, before norm and rotation (a mixer without a value projection).
+
+    `norm_unit` > 0: the norms run over units of that many columns (a head each) with gains of norm_unit
+    elements that all units share. `mix_cache` (a value cache of another layer, same shape as `v_cache`, with
+    its page table `mix_table` and ring `mix_ring`): the values are blended before they are cached,
+    v <- (1 - mix) v + mix * (the row that cache holds for the same token), in 32-bit, rounded once."""
+    _require_cuda(u, q_gain, k_gain, rope_table, tok_pos, tok_seq, q_out, block_table, k_cache, v_cache, mix_cache, mix_table)
     n = q_out.shape[0]
     if value_source is None:
         value_source = q_width + k_width
@@ -435,9 +441,16 @@ def norm_rope_cache_write(u, q_width, k_width, v_width, q_gain, k_gain, eps, rop
             or value_source < 0):
         raise KernelError(f"norm_rope_cache_write: u {tuple(u.shape)} does not hold [{n}, {q_width} + {k_width} + {v_width}]")
     _check_rows(q_out, n, q_width, u.dtype, "norm_rope_cache_write: q_out")
-    for gain, width in ((q_gain, q_width), (k_gain, k_width)):
+    if norm_unit < 0 or (norm_unit and (q_width % norm_unit or k_width % norm_unit)):
+        raise KernelError(f"norm_rope_cache_write: units of {norm_unit} columns do not divide {q_width} and {k_width}")
+    for gain, width in ((q_gain, norm_unit or q_width), (k_gain, norm_unit or k_width)):
         if gain is not None and (gain.dtype != torch.float32 or gain.numel() != width or not gain.is_contiguous()):
             raise KernelError(f"norm_rope_cache_write: a gain must be contiguous float32 [{width}]")
+    if mix_cache is not None and (mix_table is None or mix_ring < 1 or not v_width or v_cache is None
+                                  or mix_cache.dtype != v_cache.dtype or tuple(mix_cache.shape[1:]) != tuple(v_cache.shape[1:])
+                                  or not mix_cache.is_contiguous() or mix_table.shape[0] != block_table.shape[0]):
+        raise KernelError("norm_rope_cache_write: the cache whose values are blended in must have the value cache's "
+                          "head count and width, and come with its page table")
     n_rot = 0
     if rope_table is not None:
         n_rot = rope_table.shape[1]
@@ -457,7 +470,8 @@ def norm_rope_cache_write(u, q_width, k_width, v_width, q_gain, k_gain, eps, rop
           _ptr(tok_seq), _ptr(q_out), _c_int(q_out.stride(0)), _ptr(block_table), _c_int(block_table.shape[1]),
           _c_int(ring_pages), _ptr(k_cache), _c_int(k_cache.shape[1]), _ptr(v_cache if v_width else None),
           _c_int(v_cache.shape[1] if v_width else 0), _c_int(1 if write_cache else 0), _c_int(value_source),
-          _c_int(n), _stream())
+          _c_int(norm_unit), _ptr(mix_cache), _ptr(mix_table), _c_int(mix_table.shape[1] if mix_table is not None else 0),
+          _c_int(mix_ring), _c_float(mix), _c_int(n), _stream())
     return q_out
 
 
@@ -576,6 +590,55 @@ def delta_rule(proj, taps, state, tok_seq, cu_seqlens, slot_ids, rate, dt_bias, 
     return mixed
 
 
+# ----------------------------------------------------------------------------- state-space recurrence
+
+def state_space_work_width(n_heads: int, groups: int, state: int, vdim: int) -> int:
+    """Floats of a token's 32-bit work row: x, B, C behind the convolution, the step size and the decay per head."""
+    return (n_heads * vdim + 2 * groups * state + 2 * n_heads + 3) // 4 * 4
+
+
+def state_space(proj, taps, conv_bias, state, tok_seq, cu_seqlens, slot_ids, rate, dt_bias, skip, norm_weight, eps,
+                norm_groups, out_scale, work, y, mixed, n_heads, groups, n_state, vdim):
+    """A state-space recurrence with a scalar decay per head, behind its projection. `proj` [T, >= 2 H V + 2 G N + H]
+    (run dtype, rows contiguous) holds per token [z (H V) | x (H V) | B (G N) | C (G N) | dt (H)]. x, B and C pass a
+    causal convolution per channel (`taps` float32 [C, K], the last column the current token's; `conv_bias` float32
+    [C] or None) and silu; dt <- softplus(dt + dt_bias); per head (a group of B and C serves H / G heads)
+    S_t = exp(rate dt) S_(t-1) + dt B_t x_t^T and y_t = S_t^T C_t + skip x_t (`rate` float32 [H], negative; `skip`
+    float32 [H] or None). Then y silu(z), divided by its root mean square in `norm_groups` equal parts (eps), times
+    `norm_weight` float32 [H V] and `out_scale`, into `mixed` [T, H V] (run dtype). `state` float32 [slots,
+    (K - 1) C + H N V]: the convolution's last inputs, then S; read and updated for the slots of the step.
+    `work` float32 [T, state_space_work_width], `y` float32 [T, H V]: scratch."""
+    _require_cuda(proj, taps, conv_bias, state, tok_seq, cu_seqlens, slot_ids, rate, dt_bias, skip, norm_weight, work, y, mixed)
+    n = proj.shape[0]
+    H, G, N, V = n_heads, groups, n_state, vdim
+    inner = H * V
+    C = inner + 2 * G * N
+    n_taps = taps.shape[1]
+    if proj.dim() != 2 or proj.shape[1] < inner + C + H or proj.stride(1) != 1:
+        raise KernelError(f"state_space: the projection {tuple(proj.shape)} does not hold {inner + C + H} columns")
+    _check_rows(mixed, n, inner, proj.dtype, "state_space: mixed")
+    for t, shape, what in ((taps, (C, n_taps), "taps"), (conv_bias, (C,), "the convolution's bias"), (rate, (H,), "rate"),
+                           (dt_bias, (H,), "dt_bias"), (skip, (H,), "skip"), (norm_weight, (inner,), "norm weight"),
+                           (y, (n, inner), "y")):
+        if t is not None and (t.dtype != torch.float32 or tuple(t.shape) != shape or not t.is_contiguous()):
+            raise KernelError(f"state_space: {what} must be contiguous float32 {shape}")
+    width = state_space_work_width(H, G, N, V)
+    if work.dtype != torch.float32 or work.dim() != 2 or work.shape[0] < n or work.shape[1] < width or not work.is_contiguous():
+        raise KernelError(f"state_space: work must be contiguous float32 [T, >= {width}]")
+    need = (n_taps - 1) * C + H * N * V
+    if state.dtype != torch.float32 or state.dim() != 2 or state.shape[1] < need or state.stride(1) != 1:
+        raise KernelError(f"state_space: the state must be float32 [slots, >= {need}]")
+    if norm_groups < 1 or inner % norm_groups:
+        raise KernelError(f"state_space: {inner} channels cannot be normed in {norm_groups} equal parts")
+    _call("state_space", "llmb_state_space", _ptr(proj), _c_int(proj.stride(0)), _c_int(_code(proj.dtype)), _ptr(taps),
+          _ptr(conv_bias), _c_int(n_taps), _ptr(state), ctypes.c_longlong(state.stride(0)), _ptr(tok_seq), _ptr(cu_seqlens),
+          _ptr(slot_ids), _ptr(rate), _ptr(dt_bias), _ptr(skip), _ptr(norm_weight), _c_float(eps), _c_int(norm_groups),
+          _c_float(out_scale), _ptr(work), _c_int(work.shape[1]), _ptr(y), _ptr(mixed), _c_int(mixed.stride(0)), _c_int(n),
+          _c_int(cu_seqlens.numel() - 1), _c_int(H), _c_int(G), _c_int(N), _c_int(V), _stream(),
+          kernels=4 if n_taps > 1 else 3)
+    return mixed
+
+
 # ----------------------------------------------------------------------------- routed experts
 
 def routed_experts_plan_ints(n_tokens: int, top: int, n_experts: int) -> int:
@@ -597,7 +660,8 @@ def routed_experts_wide(n_tokens: int, top: int, n_experts: int, hidden: int, in
             and not tactics.is_disabled("routed_experts_wide"))
 
 
-def routed_experts(h, router, router_bias, w_up, w_down, top: int, ids, weights, order, plan, act, y, gathered=None):
+def routed_experts(h, router, router_bias, w_up, w_down, top: int, ids, weights, order, plan, act, y, gathered=None,
+                   scoring: int = 0, correction=None, pass_through: int = 0, weight_scale: float = 1.0):
     """A feed-forward of routed experts on the rows of h [T, hidden] (run dtype). Router logits
     z = router h + router_bias in 32-bit (`router` float32 [E, hidden]); the `top` largest are chosen and
     weighted by the softmax over them. Expert e: W_down,e (silu(W_gate,e h) * (W_up,e h)) with `w_up`
@@ -605,18 +669,25 @@ def routed_experts(h, router, router_bias, w_up, w_down, top: int, ids, weights,
     y[t * top + k] = weight[t, k] * expert_(chosen k)(h[t]) as float32 [T * top, hidden]; the caller adds the
     `top` rows of a token. Scratch: `ids` int32 [T * top], `weights` float32 [T * top], `order` int32 [T * top],
     `plan` int32 [routed_experts_plan_ints], `act` [T * top, F] in h's dtype, and, for the steps that
-    routed_experts_wide names, `gathered` [T * top, hidden] in h's dtype (the rows of h in the plan's order)."""
-    _require_cuda(h, router, router_bias, w_up, w_down, ids, weights, order, plan, act, y, gathered)
+    routed_experts_wide names, `gathered` [T * top, hidden] in h's dtype (the rows of h in the plan's order).
+
+    `scoring` 1: scores s = softmax(z) over all router outputs, the `top` largest of s + `correction` (float32, one
+    per output; it takes part in the choice only) are chosen, weights s / (sum of the chosen s + 1e-20).
+    `pass_through` > 0: the router has E + pass_through outputs, and the last ones are experts without matrices
+    whose result is h itself. `weight_scale` multiplies every weight."""
+    _require_cuda(h, router, router_bias, w_up, w_down, ids, weights, order, plan, act, y, gathered, correction)
     n, hidden = h.shape
     E, two_f, _ = w_up.shape
     F = two_f // 2
     if (h.stride(1) != 1 or w_up.dtype != h.dtype or w_down.dtype != h.dtype or not w_up.is_contiguous()
             or not w_down.is_contiguous() or tuple(w_up.shape) != (E, 2 * F, hidden) or tuple(w_down.shape) != (E, hidden, F)):
         raise KernelError("routed_experts: the expert matrices must be contiguous [E, 2 F, hidden] and [E, hidden, F] in h's dtype")
-    if router.dtype != torch.float32 or tuple(router.shape) != (E, hidden) or not router.is_contiguous():
-        raise KernelError(f"routed_experts: the router must be contiguous float32 [{E}, {hidden}]")
-    if router_bias is not None and (router_bias.dtype != torch.float32 or router_bias.numel() != E):
-        raise KernelError(f"routed_experts: the router's bias must be float32 [{E}]")
+    outputs = E + pass_through
+    if router.dtype != torch.float32 or tuple(router.shape) != (outputs, hidden) or not router.is_contiguous():
+        raise KernelError(f"routed_experts: the router must be contiguous float32 [{outputs}, {hidden}]")
+    for vector, what in ((router_bias, "bias"), (correction, "correction")):
+        if vector is not None and (vector.dtype != torch.float32 or vector.numel() != outputs or not vector.is_contiguous()):
+            raise KernelError(f"routed_experts: the router's {what} must be contiguous float32 [{outputs}]")
     a = n * top
     for t, dtype, count, what in ((ids, torch.int32, a, "ids"), (weights, torch.float32, a, "weights"),
                                   (order, torch.int32, a, "order"), (plan, torch.int32, routed_experts_plan_ints(n, top, E), "plan"),
@@ -631,7 +702,8 @@ def routed_experts(h, router, router_bias, w_up, w_down, top: int, ids, weights,
     _call("routed_experts", "llmb_routed_experts", _ptr(h), _c_int(h.stride(0)), _c_int(_code(h.dtype)), _ptr(router),
           _ptr(router_bias), _ptr(w_up), _ptr(w_down), _ptr(ids), _ptr(weights), _ptr(order), _ptr(plan), _ptr(act),
           _ptr(y), _ptr(gathered if wide else None), _c_int(n), _c_int(hidden), _c_int(F), _c_int(E), _c_int(top),
-          _c_int(level), _stream(), kernels=5 if wide else 4)
+          _c_int(level), _c_int(scoring), _ptr(correction), _c_int(pass_through), _c_float(weight_scale), _stream(),
+          kernels=(5 if wide else 4) + (1 if pass_through else 0))
     return y
 
 
@@ -991,7 +1063,8 @@ def attention_decode_splits(n_seqs: int, n_heads: int, n_kv_heads: int, max_len:
 
 def attention(qkv, k_cache, v_cache, block_table, ring_pages, tok_pos, tok_seq, n_heads,
               n_kv_heads, head_dim, scale, window=0, out=None, decode=False, seq_lens=None,
-              max_len=0, cu_seqlens=None, max_new=0, seq_order=None, sinks=None, gate=None, out_scale=1.0):
+              max_len=0, cu_seqlens=None, max_new=0, seq_order=None, sinks=None, gate=None, out_scale=1.0,
+              softcap=0.0, value_dim=None):
     """Causal grouped-query attention of the new tokens' queries (the first
     Hq * D columns of `qkv`) over the paged cache, which already holds the new
     tokens' keys and values. Returns [T, Hq * D] in qkv's dtype. `seq_order`
@@ -1002,14 +1075,17 @@ def attention(qkv, k_cache, v_cache, block_table, ring_pages, tok_pos, tok_seq, 
     no key and no value and is not scaled. `gate` ([T, Hq] in qkv's dtype, rows contiguous): the
     result of head a for token t is multiplied by sigmoid(gate[t, a]). `out_scale` multiplies the
     result. With any of the three, `out` may be a range of columns of a wider buffer. The value
-    cache may be the key cache itself (a mixer whose values are its keys)."""
+    cache may be the key cache itself (a mixer whose values are its keys). `softcap` > 0 bounds the scaled
+    scores before the softmax: s <- softcap * tanh(s / softcap). `value_dim` (default head_dim): the size of a
+    value where it differs from a key's; the result is then [T, Hq * value_dim] (the kernel for any sizes)."""
     _require_cuda(qkv, k_cache, v_cache, block_table, tok_pos, tok_seq, sinks, gate)
     n = qkv.shape[0]
-    extras = (sinks is not None or gate is not None or out_scale != 1.0
+    value_dim = value_dim or head_dim
+    extras = (sinks is not None or gate is not None or out_scale != 1.0 or softcap > 0.0 or value_dim != head_dim
               or (out is not None and not out.is_contiguous()))
     if extras:
         if out is not None:
-            _check_rows(out, n, n_heads * head_dim, qkv.dtype, "attention: out")
+            _check_rows(out, n, n_heads * value_dim, qkv.dtype, "attention: out")
         if sinks is not None and (sinks.dtype != torch.float32 or sinks.numel() != n_heads or not sinks.is_contiguous()):
             raise KernelError(f"attention: sinks must be contiguous float32 [{n_heads}]")
         if gate is not None:
@@ -1017,7 +1093,7 @@ def attention(qkv, k_cache, v_cache, block_table, ring_pages, tok_pos, tok_seq, 
     else:
         _check_out(out, (n, n_heads * head_dim), qkv.dtype, "attention")
     if out is None:
-        out = torch.empty((n, n_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
+        out = torch.empty((n, n_heads * value_dim), dtype=qkv.dtype, device=qkv.device)
     variant = tactics.choose_attention(decode, qkv.dtype, n_heads, n_kv_heads, head_dim, window,
                                        cu_seqlens is not None and seq_lens is not None,
                                        qkv.stride(0) % 8 == 0 and qkv.data_ptr() % 16 == 0)
@@ -1028,6 +1104,8 @@ def attention(qkv, k_cache, v_cache, block_table, ring_pages, tok_pos, tok_seq, 
                 and cu_seqlens is not None and seq_lens is not None and qkv.stride(0) % 2 == 0 and out.stride(0) % 2 == 0 \
                 and qkv.data_ptr() % 4 == 0 and out.data_ptr() % 4 == 0:
             variant = "attention_prefill"
+    if value_dim != head_dim:
+        variant = "attention_generic"                 # the tile kernels take values of the keys' size
     if variant == "attention_decode" and (qkv.stride(0) % 2 or qkv.data_ptr() % 4):
         variant = "attention_generic"
     if variant == "attention_prefill_tc":
@@ -1043,12 +1121,12 @@ def attention(qkv, k_cache, v_cache, block_table, ring_pages, tok_pos, tok_seq, 
               _c_int(ring_pages), _ptr(cu_seqlens), _ptr(seq_lens), _ptr(out), _c_int(out.stride(0)),
               _c_int(cu_seqlens.numel() - 1), _c_int(max_new), _c_int(n_heads), _c_int(n_kv_heads),
               _c_int(head_dim), _c_float(scale), _c_int(window), _ptr(sinks), _ptr(gate),
-              _c_int(gate.stride(0) if gate is not None else 0), _c_float(out_scale), _stream())
+              _c_int(gate.stride(0) if gate is not None else 0), _c_float(out_scale), _c_float(softcap), _stream())
     elif variant == "attention_decode":
         # the plain grouped-query case keeps the kernel file it was tuned in; a window, a sink, a gate, a scale, a
         # value cache that is the key cache and groups above 8 run the same kernel with those additions
         plain = (window == 0 and sinks is None and gate is None and out_scale == 1.0 and n_heads // n_kv_heads <= 8
-                 and k_cache.data_ptr() != v_cache.data_ptr())
+                 and softcap <= 0.0 and k_cache.data_ptr() != v_cache.data_ptr())
         name = "attention_decode" if plain else "attention_decode_window"
         splits = attention_decode_splits(n, n_heads, n_kv_heads, max_len, window)
         lib = load_library(name)
@@ -1071,15 +1149,16 @@ def attention(qkv, k_cache, v_cache, block_table, ring_pages, tok_pos, tok_seq, 
             _call(name, "llmb_attention_decode", *head, _c_int(splits), _stream(), kernels=2 if splits > 1 else 1)
         else:
             _call(name, "llmb_attention_decode_window", *head, _ptr(sinks), _ptr(gate),
-                  _c_int(gate.stride(0) if gate is not None else 0), _c_float(out_scale), _c_int(splits), _stream(),
-                  kernels=2 if splits > 1 else 1)
+                  _c_int(gate.stride(0) if gate is not None else 0), _c_float(out_scale), _c_float(softcap),
+                  _c_int(splits), _stream(), kernels=2 if splits > 1 else 1)
     elif variant == "attention_generic":
         _call("attention_generic", "llmb_attention_generic", _ptr(qkv), _c_int(qkv.stride(0)),
               _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _c_int(block_table.shape[1]),
               _c_int(ring_pages), _ptr(tok_pos), _ptr(tok_seq), _ptr(out), _c_int(out.stride(0)),
               _c_int(_code(qkv.dtype)), _c_int(n), _c_int(n_heads), _c_int(n_kv_heads),
               _c_int(head_dim), _c_float(scale), _c_int(window), _ptr(sinks), _ptr(gate),
-              _c_int(gate.stride(0) if gate is not None else 0), _c_float(out_scale), _stream())
+              _c_int(gate.stride(0) if gate is not None else 0), _c_float(out_scale), _c_float(softcap),
+              _c_int(value_dim), _stream())
     else:
         raise KernelError(f"attention: no kernel named {variant}")
     return out
@@ -1321,6 +1400,6 @@ def required_libraries() -> list:
 
 __all__ = ["PAGE", "GLU_BLOCK", "glu_fusable", "embed", "scale_", "random_normal_", "begin_recording", "end_recording", "RecordedPass", "scratch_generation", "Emit", "FoldedNorm", "RopeWrite", "cast_sumsq", "SUMSQ_LD", "rmsnorm", "swiglu", "rope_cache_write", "linear", "attention",
            "softcap_", "add_rows_", "conv_rope_cache_write", "diff_attention", "tanh_norm", "norm_rope_cache_write",
-           "sigmoid_attention", "gated_recurrence", "attention_replay_key", "attention_decode_splits", "sigmoid_attention_replay_key", "sigmoid_decode_splits",
+           "sigmoid_attention", "gated_recurrence", "state_space", "attention_replay_key", "attention_decode_splits", "sigmoid_attention_replay_key", "sigmoid_decode_splits",
            "argmax_rows", "sample_rows", "launch_count", "count_launches", "tensor_core_status", "check_device_status", "ensure_built", "load_library", "all_sources",
            "required_libraries", "tactics"]

@@ -16,6 +16,7 @@ from .projected import ProjectedMixer
 from .routed_experts import RoutedExperts
 from .side_by_side import SideBySideMixer
 from .sigmoid_attention import SigmoidAttentionMixer
+from .state_space import StateSpaceMixer
 from .position import Rope, inverse_frequencies
 
 __all__ = ["spec", "Block", "FeedForward", "Mixer", "Norm", "Part", "PositionEncoding",
@@ -24,4 +25,4 @@ __all__ = ["spec", "Block", "FeedForward", "Mixer", "Norm", "Part", "PositionEnc
            "register_norm", "register_position", "AttentionMixer", "DiffAttentionMixer", "ParallelBlock", "PreNormBlock", "GatedMlp",
            "RmsNorm", "Rope", "inverse_frequencies", "TanhNorm", "ProjectedMixer", "LatentAttentionMixer",
            "SigmoidAttentionMixer", "GatedRecurrenceMixer", "SideBySideMixer", "SandwichBlock", "DeltaRuleMixer",
-           "GatedAttentionMixer", "Mlp", "RoutedExperts"]
+           "GatedAttentionMixer", "Mlp", "RoutedExperts", "StateSpaceMixer"]

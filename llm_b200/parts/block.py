@@ -23,7 +23,8 @@ class PreNormBlock(Block):
     rows and scales by the norm's factor in its epilogue, and the product that last updated
     the residual (the part before, the block before, or the embedding) has left that copy and
     the rows' sums of squares. MythEclipse/llm fuses its norm into the consumer's input in the
-    same spirit (apps/engine/kernels/gpu.cu:351-407)."""
+    same spirit (apps/engine/kernels/gpu.cu:351-407). The feed-forward (with its norm) may be absent:
+    a layer that only mixes."""
 
     #: `forward` takes `normed=` and `emit_next=` (see there)
     chains_norms = True
@@ -32,12 +33,12 @@ class PreNormBlock(Block):
         self.spec = spec
         self.mixer_norm = build_norm(spec.mixer_norm)
         self.mixer = build_mixer(spec.mixer)
-        self.ffn_norm = build_norm(spec.ffn_norm)
-        self.feed_forward = build_feed_forward(spec.feed_forward)
+        self.feed_forward = build_feed_forward(spec.feed_forward) if spec.feed_forward is not None else None
+        self.ffn_norm = build_norm(spec.ffn_norm) if self.feed_forward is not None else None
 
     @property
     def parts(self):
-        return (self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward)
+        return tuple(p for p in (self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward) if p is not None)
 
     @property
     def graph_safe(self):
@@ -57,7 +58,7 @@ class PreNormBlock(Block):
         for p in self.parts:
             p.bind(tensors, dtype, device)
         self.folded_mixer = self._fold(self.mixer_norm, self.mixer, dtype)
-        self.folded_ffn = self._fold(self.ffn_norm, self.feed_forward, dtype)
+        self.folded_ffn = self.feed_forward is not None and self._fold(self.ffn_norm, self.feed_forward, dtype)
 
     folded_mixer = folded_ffn = False
 
@@ -105,7 +106,7 @@ class PreNormBlock(Block):
         from ..engine.workspace import BufferRequest
         hidden = self.spec.mixer_norm.size
         mixer = self.mixer.scratch_requests(n_tokens, dtype)
-        ffn = self.feed_forward.scratch_requests(n_tokens, dtype)
+        ffn = self.feed_forward.scratch_requests(n_tokens, dtype) if self.feed_forward is not None else []
         mixer_end = 1 + max([r.last_use for r in mixer] + [0])
         ffn_start = mixer_end + 2
         ffn_end = ffn_start + max([r.last_use for r in ffn] + [0])
@@ -119,7 +120,7 @@ class PreNormBlock(Block):
         if self.folded_ffn:
             out += [BufferRequest("h_ffn", (n_tokens, hidden), torch.bfloat16, 1, ffn_end),
                     BufferRequest("s_ffn", sums, torch.float32, 1, ffn_end)]
-        else:
+        elif self.feed_forward is not None:
             out.append(BufferRequest("h_ffn", (n_tokens, hidden), dtype, mixer_end + 1, ffn_end))
         out += [r.shifted(ffn_start, "ffn.") for r in ffn]
         return out
@@ -144,6 +145,8 @@ class PreNormBlock(Block):
         else:
             h = self.mixer_norm.forward(x, ctx.dtype, out=ctx.scratch("h_mixer", tuple(x.shape), ctx.dtype))
         emit_ffn = self._emit(ctx, "ffn", n, x.device) if self.folded_ffn else None
+        if self.feed_forward is None:                  # the mixer is the layer's last part
+            emit_ffn = emit_next
         prefixed("mixer.")
         if emit_ffn is not None and self.mixer.emits:
             self.mixer.forward(h, ctx, entry, cache_entry, x, emit=emit_ffn)
@@ -152,6 +155,8 @@ class PreNormBlock(Block):
             if emit_ffn is not None:
                 ops.cast_sumsq(x, emit_ffn)
         prefixed("")
+        if self.feed_forward is None:
+            return
         # ---- feed-forward
         if emit_ffn is not None:
             h = ops.FoldedNorm(emit_ffn.rows, emit_ffn.sumsq, emit_ffn.parts, self.spec.ffn_norm.eps,

@@ -7,7 +7,7 @@ from .. import ops
 from ..cache import KvRequest
 from ..errors import FormatError
 from ..weights.loader import ParamSpec
-from .base import build_position, register_mixer, to_run_dtype
+from .base import build_position, register_mixer, to_float32, to_run_dtype
 from .projected import ProjectedMixer
 
 
@@ -21,7 +21,13 @@ class GatedAttentionMixer(ProjectedMixer):
     values into the paged cache (ops.norm_rope_cache_write without norms; for shared values it
     reads the value rows from the key columns), the library's attention kernels (a windowed layer
     keeps a ring of pages), the gate, the output product. Rotated keys and unrotated values are both
-    cached: the attention kernels then need nothing new."""
+    cached: the attention kernels then need nothing new.
+
+    The spec's switches (all off by default) ride in the same launches: `head_norm` in the launch that rotates
+    (per-head RMS norms of queries and keys with weights the heads share), `value_mix` there too (the values are
+    blended with those the first layer of the same name cached for the same token, before they are cached),
+    `head_gate` (one gate per head), `softcap`, `unit_sink` and `out_scale` inside the attention kernels. Values
+    may be wider or narrower than keys (the cache keeps a tensor for each; the kernel for any sizes runs)."""
     libraries = ("elementwise", "gemm_simt", "gemm_skinny", "gemm_tc", "projection_norm", "post_norm",
                  "attention_generic", "attention_decode", "attention_decode_window", "attention_prefill",
                  "attention_prefill_tc")
@@ -32,10 +38,14 @@ class GatedAttentionMixer(ProjectedMixer):
             raise FormatError("a gated attention needs positive sizes, heads in whole groups and a window that is not negative")
         if s.values_are_keys and s.value_dim != s.head_dim:
             raise FormatError(f"values that are the keys have the keys' size {s.head_dim}, not {s.value_dim}")
-        if s.value_dim != s.head_dim:
-            raise FormatError("the softmax attention kernels take values of the keys' size")
+        if s.out_gate and s.head_gate:
+            raise FormatError("a gated attention has a gate per element or a gate per head, not both")
+        if s.value_mix is not None and s.values_are_keys:
+            raise FormatError("values that are the keys cannot be blended with another layer's")
         self.spec = spec
         self.position = build_position(spec.position)
+        self.q_gain = self.k_gain = self.sinks = None
+        self.mix_weight = 0.0
 
     @property
     def q_width(self):
@@ -58,24 +68,45 @@ class GatedAttentionMixer(ProjectedMixer):
         return self.q_width + self.k_width + (0 if self.spec.values_are_keys else self.v_width)
 
     @property
+    def gate_width(self):
+        s = self.spec
+        return self.out_width if s.out_gate else (s.n_heads if s.head_gate else 0)
+
+    @property
     def in_width(self):
-        return self.gate_offset + (self.out_width if self.spec.out_gate else 0)
+        return (self.gate_offset + self.gate_width + 7) // 8 * 8       # (rows of zeros fill up to a multiple of 8)
 
     def _roles(self):
         s = self.spec
-        return ["q", "k"] + ([] if s.values_are_keys else ["v"]) + (["gate"] if s.out_gate else [])
+        return ["q", "k"] + ([] if s.values_are_keys else ["v"]) + (["gate"] if s.out_gate or s.head_gate else [])
 
     def parameters(self):
         s, t = self.spec, self.spec.tensor
-        widths = {"q": self.q_width, "k": self.k_width, "v": self.v_width, "gate": self.out_width}
+        widths = {"q": self.q_width, "k": self.k_width, "v": self.v_width, "gate": self.gate_width}
         out = {t[r]: ParamSpec((widths[r], s.hidden)) for r in self._roles()}
         out[t["o"]] = ParamSpec((s.hidden, self.out_width))
+        if s.head_norm:
+            out[t["q_norm"]] = ParamSpec((s.head_dim,), "gain")
+            out[t["k_norm"]] = ParamSpec((s.head_dim,), "gain")
+        if s.value_mix is not None:
+            out[t["value_mix"]] = ParamSpec((), "gate_scalar")         # (stored, but unused, in the first such layer too)
         return out
 
     def bind(self, tensors, dtype, device):
-        t = self.spec.tensor
-        self.w_in = torch.cat([to_run_dtype(tensors[t[r]], dtype, device) for r in self._roles()]).contiguous()
+        s, t = self.spec, self.spec.tensor
+        rows = [to_run_dtype(tensors[t[r]], dtype, device) for r in self._roles()]
+        pad = self.in_width - sum(r.shape[0] for r in rows)
+        if pad:
+            rows.append(torch.zeros((pad, s.hidden), dtype=dtype, device=device))
+        self.w_in = torch.cat(rows).contiguous()
         self.w_out = to_run_dtype(tensors[t["o"]], dtype, device)
+        if s.head_norm:
+            self.q_gain = to_float32(tensors[t["q_norm"]], device)
+            self.k_gain = to_float32(tensors[t["k_norm"]], device)
+        if s.value_mix is not None:
+            self.mix_weight = float(tensors[t["value_mix"]].float())
+        if s.unit_sink:
+            self.sinks = torch.zeros(s.n_heads, dtype=torch.float32, device=device)
 
     def prepare(self, max_positions, device):
         if self.position is not None:
@@ -83,7 +114,11 @@ class GatedAttentionMixer(ProjectedMixer):
 
     def kv_request(self):
         s = self.spec
-        return KvRequest(s.n_kv_heads, s.head_dim, s.window)
+        return KvRequest(s.n_kv_heads, s.head_dim, s.window,
+                         value_dim=s.value_dim if s.value_dim != s.head_dim else None)
+
+    def mix_weights(self):
+        return [t for t in (self.q_gain, self.k_gain) if t is not None]
 
     def mix_scratch(self, n_tokens, dtype):
         from ..engine.workspace import BufferRequest
@@ -107,16 +142,30 @@ class GatedAttentionMixer(ProjectedMixer):
         queries = scratch("queries", (n, self.q_width), proj.dtype)
         if queries is None:
             queries = torch.empty((n, self.q_width), dtype=proj.dtype, device=proj.device)
-        ops.norm_rope_cache_write(proj, self.q_width, self.k_width, self.v_width, None, None, 0.0,
+        blend = {}
+        if s.value_mix is not None:
+            # the first layer of the name leaves where its values are cached; the others blend those in
+            key = ("value_mix", s.value_mix)
+            if s.value_mix_first:
+                ctx.extras[key] = (values, table, ring)
+            elif key in ctx.extras:
+                first_values, first_table, first_ring = ctx.extras[key]
+                blend = dict(mix_cache=first_values, mix_table=first_table, mix_ring=first_ring, mix=self.mix_weight)
+            else:
+                raise FormatError(f"values are blended with those of the first '{s.value_mix}' layer, which has not run")
+        ops.norm_rope_cache_write(proj, self.q_width, self.k_width, self.v_width, self.q_gain, self.k_gain, s.norm_eps,
                                   self.position.table if self.position is not None else None, s.head_dim,
                                   self.position.interleaved if self.position is not None else False,
                                   ctx.tok_pos, ctx.tok_seq, queries, table, ring, keys, values,
                                   write_cache=(entry == cache_entry),
-                                  value_source=self.q_width if s.values_are_keys else self.q_width + self.k_width)
+                                  value_source=self.q_width if s.values_are_keys else self.q_width + self.k_width,
+                                  norm_unit=s.head_dim if s.head_norm else 0, **blend)
+        gate = proj[:, self.gate_offset:self.gate_offset + s.n_heads] if s.head_gate else None
         ops.attention(queries, keys, values, table, ring, ctx.tok_pos, ctx.tok_seq, s.n_heads, s.n_kv_heads,
                       s.head_dim, s.scale, s.window, out=out, decode=ctx.decode, seq_lens=ctx.seq_lens,
                       max_len=ctx.max_len, cu_seqlens=ctx.cu_seqlens, max_new=max(ctx.new_counts),
-                      seq_order=ctx.seq_order)
+                      seq_order=ctx.seq_order, sinks=self.sinks, gate=gate, out_scale=s.out_scale, softcap=s.softcap,
+                      value_dim=s.value_dim)
         if s.out_gate:
             ops.sigmoid_gate_(out, proj[:, self.gate_offset:self.gate_offset + self.out_width])
 

@@ -24,6 +24,8 @@ def inverse_frequencies(head_dim: int, theta: float, scaling: dict | None) -> to
         return freq
     if kind == "ramp":
         return _ramp_scaled(freq, head_dim, theta, scaling)
+    if kind == "linear":                               # positions stretched by `factor`: every frequency divided by it
+        return freq / float(scaling["factor"])
     if kind != "llama3":
         raise Unsupported(f"rope scaling of type '{kind}'")
     factor = float(scaling["factor"])

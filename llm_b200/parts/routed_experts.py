@@ -20,7 +20,13 @@ class RoutedExperts(FeedForward):
     weight (tcgen05 tiles of 128 rows where a step brings many rows an expert, tiles of 32 else).
     Each (token, chosen expert) leaves a 32-bit row of its own; the sum over a token's rows, in the
     order of choice, is taken by whoever reads them (`result_terms` rows a token when written
-    fresh; else they are added into the residual here)."""
+    fresh; else they are added into the residual here).
+
+    With the spec's `scoring` 'all' the scores are the softmax over every router output, the choice is by score
+    plus a stored correction, and the weights are the chosen scores over their sum; with `pass_through` the
+    router's last outputs stand for experts without matrices that hand their input through; `out_scale`
+    multiplies the weights. All of it is the router kernel's work (and one small launch for the rows handed
+    through): the plan and the grouped products see the assignments of experts with matrices only."""
     graph_safe = True
     overwrites = True
     libraries = ("routed_experts", "post_norm")
@@ -29,10 +35,14 @@ class RoutedExperts(FeedForward):
         s = spec
         if s.activation != "silu":
             raise Unsupported(f"activation '{s.activation}' in routed experts")
-        if min(s.hidden, s.intermediate, s.n_experts, s.top) < 1 or s.top > s.n_experts:
-            raise FormatError(f"{s.top} of {s.n_experts} experts cannot be chosen")
+        if min(s.hidden, s.intermediate, s.n_experts, s.top) < 1 or s.pass_through < 0 or s.top > s.n_experts + s.pass_through:
+            raise FormatError(f"{s.top} of {s.n_experts + max(s.pass_through, 0)} experts cannot be chosen")
+        if s.scoring not in ("chosen", "all"):
+            raise Unsupported(f"scoring '{s.scoring}' in routed experts (built: 'chosen', 'all')")
+        if s.correction and s.scoring != "all":
+            raise Unsupported("a correction of the choice needs scores over all experts")
         self.spec = spec
-        self.router = self.router_bias = self.w_up = self.w_down = None
+        self.router = self.router_bias = self.correction = self.w_up = self.w_down = None
 
     @property
     def result_terms(self):
@@ -40,9 +50,12 @@ class RoutedExperts(FeedForward):
 
     def parameters(self):
         s, t = self.spec, self.spec.tensor
-        out = {t["router"]: ParamSpec((s.n_experts, s.hidden))}
+        outputs = s.n_experts + s.pass_through
+        out = {t["router"]: ParamSpec((outputs, s.hidden))}
         if s.router_bias:
-            out[t["router_bias"]] = ParamSpec((s.n_experts,), "bias")
+            out[t["router_bias"]] = ParamSpec((outputs,), "bias")
+        if s.correction:
+            out[t["correction"]] = ParamSpec((outputs,), "bias")
         for e in range(s.n_experts):
             names = s.expert_tensor(e)
             out[names["gate"]] = ParamSpec((s.intermediate, s.hidden))
@@ -54,6 +67,7 @@ class RoutedExperts(FeedForward):
         s, t = self.spec, self.spec.tensor
         self.router = to_float32(tensors[t["router"]], device)          # the router is 32-bit in every run
         self.router_bias = to_float32(tensors[t["router_bias"]], device) if s.router_bias else None
+        self.correction = to_float32(tensors[t["correction"]], device) if s.correction else None
         ups, downs = [], []
         for e in range(s.n_experts):
             names = s.expert_tensor(e)
@@ -99,7 +113,8 @@ class RoutedExperts(FeedForward):
         wide = ops.routed_experts_wide(n, s.top, s.n_experts, s.hidden, s.intermediate, h.dtype)
         gathered = buffer("expert_in", (a, s.hidden), h.dtype) if wide else None
         ops.routed_experts(h, self.router, self.router_bias, self.w_up, self.w_down, s.top, ids, weights, order, plan,
-                           act, rows, gathered)
+                           act, rows, gathered, scoring=1 if s.scoring == "all" else 0, correction=self.correction,
+                           pass_through=s.pass_through, weight_scale=s.out_scale)
         if not fresh:
             ops.add_terms_(residual, rows, s.top)
 

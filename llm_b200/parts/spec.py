@@ -175,7 +175,17 @@ class GatedAttentionSpec:
     """Grouped-query softmax attention whose result is multiplied, element by element, by
     sigmoid(W_g h) before the output projection (`out_gate`; the gate reads the mixer's input). With
     `values_are_keys` there is no value projection: a key head's values are its keys as projected,
-    before the rotation (so value_dim == head_dim)."""
+    before the rotation (so value_dim == head_dim).
+
+    Switches that are off by default: `head_norm` (every head of the queries and of the keys is divided by its
+    own root mean square over head_dim (eps `norm_eps`) and multiplied by a weight of head_dim elements that the
+    heads share, before the rotation); `head_gate` (one gate number per head, sigmoid(W_g h)[head] with W_g
+    [n_heads, hidden], instead of one per element); `softcap` (c > 0: score <- c tanh(score / c) behind the
+    scale); `unit_sink` (the softmax's denominator holds one more term e^0 that has no value);
+    `value_mix` (a name shared by the layers whose values are blended: in every such layer but the one with
+    `value_mix_first`, v <- (1 - w) v + w v_first with w one stored number (role `value_mix`) and v_first the
+    values that the first such layer computed for the same token; the blended values are what is cached);
+    `out_scale` multiplies the mixer's result."""
     hidden: int
     n_heads: int
     n_kv_heads: int
@@ -186,8 +196,16 @@ class GatedAttentionSpec:
     values_are_keys: bool
     out_gate: bool
     position: Optional[PositionSpec]
-    names: tuple                     # sorted (role, tensor name): q, k, o (+ v, gate)
+    names: tuple                     # sorted (role, tensor name): q, k, o (+ v, gate, q_norm, k_norm, value_mix)
     kind: str = "gated_attention"
+    head_norm: bool = False
+    norm_eps: float = 0.0
+    head_gate: bool = False
+    softcap: float = 0.0
+    unit_sink: bool = False
+    value_mix: Optional[str] = None
+    value_mix_first: bool = False
+    out_scale: float = 1.0
 
     @property
     def tensor(self):
@@ -213,6 +231,31 @@ class DeltaRuleSpec:
     names: tuple                     # sorted (role, tensor name): q, k, v, q_conv, k_conv, v_conv, beta, decay, a_log, dt_bias, gate, norm, o
     unit_eps: float = 1e-6
     kind: str = "delta_rule"
+
+    @property
+    def tensor(self):
+        return dict(self.names)
+
+
+@dataclass(frozen=True)
+class StateSpaceSpec:
+    """A state-space recurrence with one scalar decay per head (the layer of Dao and Gu's "Transformers are
+    SSMs"): W_in h = [z | x | B | C | dt] with x of n_heads heads of value_dim, B and C of `groups` groups of
+    `state` elements (a group serves n_heads / groups heads); x, B, C pass one causal convolution per channel
+    (`conv_taps` taps, a bias) and silu; dt <- softplus(dt + dt_bias); per head S_t = exp(-exp(A_log) dt) S_(t-1)
+    + dt B_t x_t^T, y_t = S_t^T C_t + D x_t; y silu(z) is divided by its root mean square in `norm_groups` equal
+    parts (eps), multiplied by a weight per channel, then W_o. `out_scale` multiplies the result."""
+    hidden: int
+    n_heads: int
+    value_dim: int
+    state: int
+    groups: int
+    conv_taps: int
+    norm_groups: int
+    eps: float
+    names: tuple                     # sorted (role, tensor name): in, conv, conv_bias, dt_bias, a_log, skip, norm, o
+    out_scale: float = 1.0
+    kind: str = "state_space"
 
     @property
     def tensor(self):
@@ -259,16 +302,26 @@ class RoutedExpertsSpec:
     """A mixture of `n_experts` gated feed-forwards of which a token uses `top`: router logits
     W_r h (+ bias) in 32-bit, the `top` largest chosen, their weights the softmax over the chosen
     logits; expert e is down_e(silu(gate_e h) * (up_e h)). `expert_names` holds the (role, name)
-    pairs of one expert with '{e}' in place of its index."""
+    pairs of one expert with '{e}' in place of its index.
+
+    `scoring` 'all' instead: scores s = softmax over ALL router outputs, the `top` largest of s + correction
+    (`correction`: a stored vector that takes part in the choice only) are chosen, and the weights are the
+    chosen scores divided by their sum (+ 1e-20). `pass_through` > 0: the router has n_experts + pass_through
+    outputs; the last ones are experts without tensors whose result is their input. `out_scale` multiplies
+    the result."""
     hidden: int
     intermediate: int
     n_experts: int
     top: int
     router_bias: bool
-    names: tuple                     # sorted (role, tensor name): router (+ router_bias)
+    names: tuple                     # sorted (role, tensor name): router (+ router_bias, correction)
     expert_names: tuple              # sorted (role, pattern): gate, up, down
     activation: str = "silu"
     kind: str = "routed_experts"
+    scoring: str = "chosen"          # 'chosen': softmax over the chosen logits; 'all': see above
+    correction: bool = False
+    pass_through: int = 0
+    out_scale: float = 1.0
 
     @property
     def tensor(self):
