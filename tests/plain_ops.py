@@ -127,11 +127,14 @@ def rope_cache_write(qkv, rope_table, tok_pos, tok_seq, block_table, ring_pages,
 
 def attention(qkv, k_cache, v_cache, block_table, ring_pages, tok_pos, tok_seq, n_heads,
               n_kv_heads, head_dim, scale, window=0, out=None, decode=False, seq_lens=None,
-              max_len=0, cu_seqlens=None, max_new=0, seq_order=None, sinks=None, gate=None, out_scale=1.0):
+              max_len=0, cu_seqlens=None, max_new=0, seq_order=None, sinks=None, gate=None, out_scale=1.0,
+              softcap=0.0, value_dim=None):
     """`sinks` (float32 [heads]): e^sink is one more term of a head's softmax denominator. `gate`
-    ([T, heads]): head a of token t is multiplied by sigmoid(gate[t, a]). `out_scale` multiplies all."""
+    ([T, heads]): head a of token t is multiplied by sigmoid(gate[t, a]). `out_scale` multiplies all.
+    `softcap` c > 0: score <- c tanh(score / c). `value_dim`: the size of a value (default head_dim)."""
     n = qkv.shape[0]
-    result = torch.zeros((n, n_heads * head_dim), dtype=torch.float32, device=qkv.device)
+    value_dim = value_dim or head_dim
+    result = torch.zeros((n, n_heads * value_dim), dtype=torch.float32, device=qkv.device)
     group = n_heads // n_kv_heads
     table = block_table.long()
     for t in range(n):
@@ -144,6 +147,8 @@ def attention(qkv, k_cache, v_cache, block_table, ring_pages, tok_pos, tok_seq, 
         q = qkv[t, :n_heads * head_dim].to(torch.float32).view(n_heads, head_dim)
         for h in range(n_heads):
             scores = (keys[:, h // group, :] @ q[h]) * scale
+            if softcap > 0.0:
+                scores = softcap * torch.tanh(scores / softcap)
             if sinks is None:
                 p = torch.softmax(scores, dim=0)
             else:
@@ -153,7 +158,7 @@ def attention(qkv, k_cache, v_cache, block_table, ring_pages, tok_pos, tok_seq, 
             o = (p @ vals[:, h // group, :]) * out_scale
             if gate is not None:
                 o = o * torch.sigmoid(gate[t, h].to(torch.float32))
-            result[t, h * head_dim:(h + 1) * head_dim] = o
+            result[t, h * value_dim:(h + 1) * value_dim] = o
     if out is not None:
         out.copy_(result.to(out.dtype))
         return out
@@ -175,11 +180,13 @@ def tanh_norm(x, alpha, gain, bias, out_dtype, rows=None, out=None, second=None)
 
 def norm_rope_cache_write(u, q_width, k_width, v_width, q_gain, k_gain, eps, rope_table, rot_unit, interleaved,
                           tok_pos, tok_seq, q_out, block_table, ring_pages, k_cache, v_cache, write_cache=True,
-                          value_source=None):
+                          value_source=None, norm_unit=0, mix_cache=None, mix_table=None, mix_ring=0, mix=0.0):
     """The first q_width columns of u are the queries, the next k_width the keys, the next v_width
     the values (or, with value_source, the v_width columns from there on: q_width makes the values
     the keys as projected). With a gain, queries (keys) are divided by the root mean square of the
-    whole segment and multiplied by the gain; then every unit of rot_unit columns of both rotates."""
+    whole segment (or, with norm_unit, of every unit of that many columns, all units sharing a gain of
+    that size) and multiplied by the gain; then every unit of rot_unit columns of both rotates. With
+    mix_cache the values become (1 - mix) v + mix * (what that cache holds at the token's place)."""
     n = u.shape[0]
     if n == 0:
         return q_out
@@ -187,7 +194,10 @@ def norm_rope_cache_write(u, q_width, k_width, v_width, q_gain, k_gain, eps, rop
 
     def segment(first, width, gain):
         x = u[:, first:first + width].to(torch.float32)
-        if gain is not None:
+        if gain is not None and norm_unit:
+            x = x.reshape(n, -1, norm_unit)
+            x = (x / torch.sqrt((x * x).mean(dim=-1, keepdim=True) + eps) * gain).reshape(n, width)
+        elif gain is not None:
             x = x / torch.sqrt((x * x).mean(dim=-1, keepdim=True) + eps) * gain
         if rope_table is not None:
             half = rope_table.shape[1] // 2
@@ -202,8 +212,11 @@ def norm_rope_cache_write(u, q_width, k_width, v_width, q_gain, k_gain, eps, rop
         k_cache[pages, :, rows, :] = k.reshape(n, k_cache.shape[1], k_cache.shape[3]).to(k_cache.dtype)
         if v_width:
             start = q_width + k_width if value_source is None else value_source
-            v = u[:, start:start + v_width]
-            v_cache[pages, :, rows, :] = v.reshape(n, v_cache.shape[1], v_cache.shape[3]).to(v_cache.dtype)
+            v = u[:, start:start + v_width].reshape(n, v_cache.shape[1], v_cache.shape[3])
+            if mix_cache is not None:
+                first_pages = mix_table.long()[tok_seq.long(), (pos // PAGE) % mix_ring]
+                v = (1.0 - mix) * v.to(torch.float32) + mix * mix_cache[first_pages, :, rows, :].to(torch.float32)
+            v_cache[pages, :, rows, :] = v.to(v_cache.dtype)
     return q_out
 
 
@@ -365,27 +378,89 @@ def routed_experts_wide(n_tokens, top, n_experts, hidden, intermediate, dtype):
     return False
 
 
-def routed_experts(h, router, router_bias, w_up, w_down, top, ids, weights, order, plan, act, y, gathered=None):
+def routed_experts(h, router, router_bias, w_up, w_down, top, ids, weights, order, plan, act, y, gathered=None,
+                   scoring=0, correction=None, pass_through=0, weight_scale=1.0):
     """Token by token: 32-bit router logits, the `top` largest, the softmax over them, and one row
-    weight * expert(h) per choice, in the order of choice (largest logit first)."""
+    weight * expert(h) per choice, in the order of choice (largest logit first). scoring 1: the scores are the
+    softmax over all outputs, the choice is by score + correction, the weights are the chosen scores over
+    their sum (+ 1e-20). The router's last `pass_through` outputs are experts whose result is h."""
     n, hidden = h.shape
     F = w_up.shape[1] // 2
     x = h.to(torch.float32)
     logits = x @ router.T
     if router_bias is not None:
         logits = logits + router_bias
+    E = w_up.shape[0]
     for t in range(n):
-        chosen = torch.topk(logits[t], top).indices
-        share = torch.softmax(logits[t, chosen], 0)
+        if scoring == 1:
+            scores = torch.softmax(logits[t], 0)
+            choice = scores + correction if correction is not None else scores
+            chosen = torch.sort(choice, descending=True, stable=True).indices[:top]
+            share = scores[chosen] / (scores[chosen].sum() + 1e-20) * weight_scale
+        else:
+            chosen = torch.topk(logits[t], top).indices
+            share = torch.softmax(logits[t, chosen], 0) * weight_scale
         for k in range(top):
             e = int(chosen[k])
+            ids[t * top + k] = e
+            weights[t * top + k] = share[k]
+            if e >= E:
+                y[t * top + k] = share[k] * x[t]
+                continue
             gate_up = x[t] @ w_up[e].to(torch.float32).T
             g, u = gate_up[:F], gate_up[F:]
             a = (g / (1.0 + torch.exp(-g)) * u).to(h.dtype).to(torch.float32)
             y[t * top + k] = share[k] * (a @ w_down[e].to(torch.float32).T)
-            ids[t * top + k] = e
-            weights[t * top + k] = share[k]
     return y
+
+
+def state_space_work_width(n_heads, groups, state, vdim):
+    return (n_heads * vdim + 2 * groups * state + 2 * n_heads + 3) // 4 * 4
+
+
+def state_space(proj, taps, conv_bias, state, tok_seq, cu_seqlens, slot_ids, rate, dt_bias, skip, norm_weight, eps,
+                norm_groups, out_scale, work, y, mixed, n_heads, groups, n_state, vdim):
+    """Sequence by sequence, token by token, head by head. A token's row of proj is
+    [z (H V) | x (H V) | B (G N) | C (G N) | dt (H) | ...]; a slot's row of state is the convolution's last
+    K - 1 inputs [K - 1, C] (oldest first, C = H V + 2 G N), then S [H, N, V]."""
+    H, G, N, V = n_heads, groups, n_state, vdim
+    n = proj.shape[0]
+    if n == 0:
+        return mixed
+    inner = H * V
+    C, K = inner + 2 * G * N, taps.shape[1]
+    cu = cu_seqlens.tolist()
+    result = torch.zeros((n, inner), dtype=torch.float32, device=proj.device)
+
+    def silu(z):
+        return z / (1.0 + torch.exp(-z))
+
+    for b in range(len(cu) - 1):
+        slot = int(slot_ids[b])
+        history = state[slot, :(K - 1) * C].view(K - 1, C).clone()
+        S = state[slot, (K - 1) * C:(K - 1) * C + H * N * V].view(H, N, V).clone()
+        for t in range(cu[b], cu[b + 1]):
+            row = proj[t].to(torch.float32)
+            rows = torch.cat([history, row[None, inner:inner + C]])                       # [K, C]
+            u = (taps.T * rows).sum(dim=0)
+            u = silu(u + conv_bias if conv_bias is not None else u)
+            history = rows[1:]
+            x, B, Cm = u[:inner].view(H, V), u[inner:inner + G * N].view(G, N), u[inner + G * N:].view(G, N)
+            z = row[inner + C:inner + C + H] + dt_bias
+            dt = torch.where(z > 20.0, z, torch.log1p(torch.exp(torch.clamp(z, max=20.0))))
+            decay = torch.exp(rate * dt)
+            out = torch.zeros((H, V), dtype=torch.float32, device=proj.device)
+            for a in range(H):
+                g = a // (H // G)
+                S[a] = decay[a] * S[a] + dt[a] * torch.outer(B[g], x[a])
+                out[a] = S[a].T @ Cm[g] + (skip[a] * x[a] if skip is not None else 0.0)
+            gated = (out.reshape(inner) * silu(row[:inner])).view(norm_groups, inner // norm_groups)
+            gated = gated / torch.sqrt((gated * gated).mean(-1, keepdim=True) + eps)
+            result[t] = gated.reshape(inner) * norm_weight * out_scale
+        state[slot, :(K - 1) * C] = history.reshape(-1)
+        state[slot, (K - 1) * C:(K - 1) * C + H * N * V] = S.reshape(-1)
+    mixed.copy_(result.to(mixed.dtype))
+    return mixed
 
 
 def softcap_(x, cap):
@@ -596,7 +671,8 @@ OPS = {"embed": embed, "scale_": scale_, "cast_sumsq": cast_sumsq, "rmsnorm": rm
        "sample_rows": sample_rows, "norm_add_": norm_add_, "gelu_": gelu_, "sigmoid_gate_": sigmoid_gate_,
        "add_terms_": add_terms_, "fill_": fill_, "delta_rule": delta_rule, "delta_rule_work_width": delta_rule_work_width,
        "routed_experts": routed_experts, "routed_experts_plan_ints": routed_experts_plan_ints,
-       "routed_experts_wide": routed_experts_wide}
+       "routed_experts_wide": routed_experts_wide, "state_space": state_space,
+       "state_space_work_width": state_space_work_width}
 
 
 def install(monkeypatch):

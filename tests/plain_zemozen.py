@@ -99,11 +99,11 @@ def rotate(x, position, freq, interleaved):
 
 # ----------------------------------------------------------------------------- mixers
 
-def attention_mixer(h, m, w, p, eps, interleaved, v_first=None, values_out=None):
+def attention_mixer(h, m, w, p, eps, interleaved, v_first=None, values_out=None, one_more=False):
     """h [T, width] of one sequence from position 0. m: the mixer's sizes; w: tensors; p: name prefix.
     `v_first` [T, G, V]: the values to blend in (None: none). `values_out` (a list) receives this layer's
-    values as projected. Switches read from m: a soft cap on the scores, a one in the softmax's
-    denominator (with the cap, as the design pairs them), a gate per head where the tensor exists."""
+    values as projected. `one_more`: the softmax's denominator holds a one besides the keys' terms. From m: a
+    soft cap on the scores where it names one; a gate per head where the tensor exists."""
     T = h.shape[0]
     H, G, D, V = int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"])
     q = (h @ w[p + "q"].T).view(T, H, D)
@@ -125,7 +125,6 @@ def attention_mixer(h, m, w, p, eps, interleaved, v_first=None, values_out=None)
     window = int(m["mask"]["size"]) if m.get("mask") else 0
     scale = float(m["scale"])
     cap = float(m["softcap"]) if m.get("softcap") else 0.0
-    one_more = bool(m.get("_sink"))
     out = torch.zeros(T, H, V, dtype=F)
     for t in range(T):
         first = max(0, t - window + 1) if window else 0
@@ -227,8 +226,7 @@ def forward(config, w, tokens, layers_out=None, margins=None):
             else:
                 y = attention_mixer(h, m, w, p + "mix.", eps, False)
         elif layer["type"] == "parallel":
-            left = dict(m["left"], _sink=True)
-            y = float(m["left_scale"]) * attention_mixer(h, left, w, p + "mix.left.", eps, True) + \
+            y = float(m["left_scale"]) * attention_mixer(h, m["left"], w, p + "mix.left.", eps, True, one_more=True) + \
                 float(m["right_scale"]) * state_space_mixer(h, m["right"], w, p + "mix.right.", eps)
         else:
             raise ValueError(layer["type"])
