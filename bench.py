@@ -1,7 +1,7 @@
 """Decode and prefill throughput of the library on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl reference]
-    python bench.py --workload llama-2-7b | llama-3.2-1b | 8b-decode512 | guberax | mefolorn | zogapel
+    python bench.py --workload llama-2-7b | llama-3.2-1b | 8b-decode512 | guberax | mefolorn | zogapel | zemozen
 
 The default run has the layer sizes of a Llama-3.1-8B (32 layers, hidden 4096,
 32 heads over 8 kv heads of 128, feed-forward 14336, vocabulary 128256, llama3
@@ -14,7 +14,7 @@ tokens and 128 new tokens each, a Llama-3.2-1B shape with 64 prompts of 1 to 8,1
 256 new tokens at temperature 0.7 (both through `LLM.generate`, host ids in and out), and the
 Llama-3.1-8B shape decoding 256 tokens after prompts of 512 at batch 1, 8 and 64; `guberax`
 times the Guberax architecture beside Llama at equal layer sizes, `mefolorn` the Mefolorn
-architecture beside both, `zogapel` the Zogapel architecture beside Mefolorn and Llama. The test names follow the `pp`/`tg`
+architecture beside both, `zogapel` the Zogapel architecture beside Mefolorn and Llama, `zemozen` the Zemozen architecture beside Zogapel and Llama. The test names follow the `pp`/`tg`
 split of MythEclipse/llm's bench (apps/cli/src/bench.rs:10-12): prefill alone,
 and decoding alone on a cache that is already filled.
 """
@@ -470,9 +470,28 @@ def workload_zogapel(args):
                    "32/16 heads of 64; vocabulary 128256; windows 2048")
 
 
+def workload_zemozen(args):
+    """Zemozen beside Zogapel (the library's closest model: windowed gated attention, a recurrence with a matrix
+    state behind a short convolution, routed experts) and Llama at equal layer sizes (the Llama-3.1-8B and
+    Llama-3.2-1B shapes), `--layers` layers of each (at most 8) plus the head. Both run with windows of 2,048;
+    Zemozen's layers alternate between its attention and its side-by-side mixer, all with 8 of 32 + 2 routed
+    experts that together are as wide as the dense feed-forward."""
+    from llm_b200.shapes import shape
+    layers = min(args.layers, 8)
+    sizes = [(size, [("llama", shape(llama, layers)), ("zogapel_window2048", shape(zogapel, layers, 2048)),
+                     ("zemozen_window2048", shape(zemozen, layers, 2048))])
+             for size, llama, zogapel, zemozen in (("1b", "llama-3.2-1b", "zogapel-1b", "zemozen-1b"),
+                                                   ("8b", "llama-3.1-8b", "zogapel-8b", "zemozen-8b"))]
+    return _beside(args, sizes, "prefill and decode tokens/s, Zemozen beside Zogapel and Llama at equal layer sizes, bf16",
+                   "zemozen_window2048-8b",
+                   "8b: width 4096, 32/8 heads of 128, 8 of 32 + 2 experts of 1792, state space 64 heads of 64 with states "
+                   "of 128 in 8 groups, 4 taps; 1b: width 2048, 32/8 heads of 64, experts of 1024, state space 32 heads; "
+                   "vocabulary 128256; windows 2048")
+
+
 WORKLOADS = {"llama-2-7b": workload_llama_2_7b, "llama-3.2-1b": workload_llama_3_2_1b,
              "8b-decode512": workload_8b_decode512, "guberax": workload_guberax, "mefolorn": workload_mefolorn,
-             "zogapel": workload_zogapel}
+             "zogapel": workload_zogapel, "zemozen": workload_zemozen}
 
 
 

@@ -92,6 +92,29 @@ SHAPES["zogapel-8b"] = _zogapel(4096, 32, 8, 128, 14336, 128256, 32, 2048, 32, 8
 SHAPES["zogapel-1b"] = _zogapel(2048, 32, 8, 64, 8192, 128256, 16, 2048, 32, 8)
 
 
+def _zemozen(width, heads, kv_heads, dim, ff, vocab, layers, window, experts, through, top):
+    """A Zemozen configuration whose layers match a Llama shape in size (width, heads, head size, vocabulary):
+    windowed attention with head norms, a gate per head and blended values in turn with the side-by-side mixer
+    (a soft-capped attention with the Llama shape's heads; a state-space recurrence as wide as the model: heads of
+    64 with states of 128 rows in 8 groups, four taps), every layer with routed experts whose `top` chosen ones
+    together are as wide as the Llama shape's feed-forward, `through` of the router's outputs handing through."""
+    attention = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "mask": {"size": window},
+                 "rot": {"base": 500000.0, "dims": dim, "scaling": {"factor": 8.0}}, "v_mix": True}
+    left = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "mask": {"size": window},
+            "rot": {"base": 20000.0, "dims": dim}, "softcap": 30.0}
+    right = {"heads": width // 64, "groups": 8, "vdim": 64, "state": 128, "conv": 4, "norm_groups": 8}
+    routed = {"kind": "moe", "router": {"experts": experts, "identity": through, "top": top}, "expert": {"ff": ff // top}}
+    kinds = [{"type": "attention", "mixer": attention, "mlp": routed},
+             {"type": "parallel", "mixer": {"left": left, "right": right, "left_scale": 0.6, "right_scale": 0.9}, "mlp": routed}]
+    return {"architecture": "Zemozen", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},
+            "residual_mult": 0.3, "layers": [kinds[i % 2] for i in range(layers)]}
+
+
+# the layer sizes of llama-3.1-8b and llama-3.2-1b; windows of 2,048 unless a run sets another; 8 of 32 + 2 experts
+SHAPES["zemozen-8b"] = _zemozen(4096, 32, 8, 128, 14336, 128256, 32, 2048, 32, 2, 8)
+SHAPES["zemozen-1b"] = _zemozen(2048, 32, 8, 64, 8192, 128256, 16, 2048, 32, 2, 8)
+
+
 def shape(name: str, layers: int | None = None, window: int | None = None) -> dict:
     """A copy of the named shape's config.json, optionally with fewer layers (and, for a shape
     with windowed attention, another window)."""

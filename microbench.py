@@ -154,7 +154,7 @@ def phase_sums(fn, label: str) -> int:
 
 def main(argv=None) -> int:
     p = argparse.ArgumentParser(description=__doc__.split("\n")[0])
-    p.add_argument("op", choices=["delta_rule", "gated_recurrence", "routed_experts", "norm_add",
+    p.add_argument("op", choices=["delta_rule", "gated_recurrence", "state_space", "routed_experts", "norm_add",
                                   "linear", "attention_decode", "attention_prefill", "rmsnorm",
                                   "swiglu", "rope", "sample"])
     p.add_argument("--m", type=int, default=8, help="rows (tokens)")
@@ -349,6 +349,29 @@ def main(argv=None) -> int:
                                              rate, state, seq, cu, slots, out, 1.0, work,
                                              single_tokens=t == 1), args, moved, 4.0 * n * channels * part,
                 f"gated_recurrence {b} x {t} tokens, {channels} channels in {blocks} blocks")
+    elif args.op == "state_space":
+        # `--batch` sequences bring `--tokens` tokens each (1: a decode step): `--heads` heads of `--head-dim` values with
+        # states of `--n` rows in `--kv-heads` groups, four taps
+        from llm_b200 import ops
+        b, t = args.batch, args.tokens
+        n = b * t
+        seq = torch.arange(b, dtype=torch.int32, device=DEV).repeat_interleave(t)
+        cu = torch.arange(b + 1, dtype=torch.int32, device=DEV) * t
+        slots = torch.arange(b, dtype=torch.int32, device=DEV)
+        H, G, N, V, K = args.heads, args.kv_heads, args.n, args.head_dim, 4
+        inner = H * V
+        C = inner + 2 * G * N
+        proj = torch.randn(n, (inner + C + H + 7) // 8 * 8, device=DEV).to(bf16)
+        taps, conv_b = torch.randn(C, K, device=DEV) / 2, torch.zeros(C, device=DEV)
+        state = torch.zeros(b, (K - 1) * C + H * N * V, device=DEV)
+        rate, dt_bias, skip = -torch.ones(H, device=DEV), torch.zeros(H, device=DEV), torch.ones(H, device=DEV)
+        weight = torch.ones(inner, device=DEV)
+        work = torch.empty(n, ops.state_space_work_width(H, G, N, V), device=DEV)
+        y, mixed = torch.empty(n, inner, device=DEV), torch.empty(n, inner, device=DEV, dtype=bf16)
+        moved = proj.numel() * 2 + work.numel() * 8 + y.numel() * 8 + mixed.numel() * 2 + state.numel() * 8
+        run(lambda: ops.state_space(proj, taps, conv_b, state, seq, cu, slots, rate, dt_bias, skip, weight, 1e-5, 8, 1.0, work, y,
+                                    mixed, H, G, N, V), args, moved, 5.0 * n * H * N * V,
+            f"state_space {b} x {t} tokens, {H} heads of {V} with states of {N} in {G} groups")
     elif args.op == "routed_experts":
         # `--m` tokens, width `--k`, `--experts` experts of `--n`, `--top` chosen; weights rotate only across experts
         from llm_b200 import ops
