@@ -606,7 +606,7 @@ def state_space(proj, taps, conv_bias, state, tok_seq, cu_seqlens, slot_ids, rat
     S_t = exp(rate dt) S_(t-1) + dt B_t x_t^T and y_t = S_t^T C_t + skip x_t (`rate` float32 [H], negative; `skip`
     float32 [H] or None). Then y silu(z), divided by its root mean square in `norm_groups` equal parts (eps), times
     `norm_weight` float32 [H V] and `out_scale`, into `mixed` [T, H V] (run dtype). `state` float32 [slots,
-    (K - 1) C + H N V]: the convolution's last inputs, then S; read and updated for the slots of the step.
+    (K - 1) C + H V N]: the convolution's last inputs, then S as [H, V, N]; read and updated for the slots of the step.
     `work` float32 [T, state_space_work_width], `y` float32 [T, H V]: scratch."""
     _require_cuda(proj, taps, conv_bias, state, tok_seq, cu_seqlens, slot_ids, rate, dt_bias, skip, norm_weight, work, y, mixed)
     n = proj.shape[0]

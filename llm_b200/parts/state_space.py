@@ -21,7 +21,7 @@ class StateSpaceMixer(ProjectedMixer):
     One product (rows padded to a multiple of 8), then ops.state_space (the convolution with its state, the
     step sizes and decays, the scan over each sequence's tokens, the gate and the grouped norm), then the
     output product. Per sequence the cache holds one float32 row: the convolution's last taps - 1 inputs
-    [taps - 1, C], then S [heads, state, value_dim]; zeroed when a slot is taken. Everything behind the
+    [taps - 1, C], then S [heads, value_dim, state]; zeroed when a slot is taken. Everything behind the
     projection is 32-bit in every run."""
     libraries = ("elementwise", "gemm_simt", "gemm_skinny", "gemm_tc", "state_space")
 

@@ -422,7 +422,7 @@ def state_space(proj, taps, conv_bias, state, tok_seq, cu_seqlens, slot_ids, rat
                 norm_groups, out_scale, work, y, mixed, n_heads, groups, n_state, vdim):
     """Sequence by sequence, token by token, head by head. A token's row of proj is
     [z (H V) | x (H V) | B (G N) | C (G N) | dt (H) | ...]; a slot's row of state is the convolution's last
-    K - 1 inputs [K - 1, C] (oldest first, C = H V + 2 G N), then S [H, N, V]."""
+    K - 1 inputs [K - 1, C] (oldest first, C = H V + 2 G N), then S [H, V, N] (a value element's N rows together)."""
     H, G, N, V = n_heads, groups, n_state, vdim
     n = proj.shape[0]
     if n == 0:
@@ -438,7 +438,7 @@ def state_space(proj, taps, conv_bias, state, tok_seq, cu_seqlens, slot_ids, rat
     for b in range(len(cu) - 1):
         slot = int(slot_ids[b])
         history = state[slot, :(K - 1) * C].view(K - 1, C).clone()
-        S = state[slot, (K - 1) * C:(K - 1) * C + H * N * V].view(H, N, V).clone()
+        S = state[slot, (K - 1) * C:(K - 1) * C + H * N * V].view(H, V, N).transpose(1, 2).clone()       # as [H, N, V]
         for t in range(cu[b], cu[b + 1]):
             row = proj[t].to(torch.float32)
             rows = torch.cat([history, row[None, inner:inner + C]])                       # [K, C]
@@ -458,7 +458,7 @@ def state_space(proj, taps, conv_bias, state, tok_seq, cu_seqlens, slot_ids, rat
             gated = gated / torch.sqrt((gated * gated).mean(-1, keepdim=True) + eps)
             result[t] = gated.reshape(inner) * norm_weight * out_scale
         state[slot, :(K - 1) * C] = history.reshape(-1)
-        state[slot, (K - 1) * C:(K - 1) * C + H * N * V] = S.reshape(-1)
+        state[slot, (K - 1) * C:(K - 1) * C + H * N * V] = S.transpose(1, 2).reshape(-1)
     mixed.copy_(result.to(mixed.dtype))
     return mixed
 
