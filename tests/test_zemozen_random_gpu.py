@@ -18,7 +18,7 @@ from tiny_zemozen import random_weights, write_folder
 pytestmark = pytest.mark.gpu
 
 DEV = "cuda:0"
-MARGIN = 0.004
+MARGIN = 0.03           # of choice scores: what bfloat16 rounding of the router's input reaches where one score dominates
 
 
 def draw_config(rng) -> dict:
@@ -60,7 +60,7 @@ def draw_config(rng) -> dict:
         experts = rng.choice([1, 2, 3, 8, 16, 40])
         identity = rng.choice([0, 0, 1, 2, 3])
         outputs = experts + identity
-        top = rng.choice([1, 2, min(4, outputs), outputs if outputs <= 8 else 6])
+        top = min(outputs, rng.choice([1, 2, 4, outputs if outputs <= 8 else 6]))
         router = {"experts": experts, "top": top}
         if identity or rng.random() < 0.5:
             router["identity"] = identity
