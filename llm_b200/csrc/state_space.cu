@@ -97,7 +97,7 @@ __device__ __forceinline__ void copies_commit() { asm volatile("cp.async.commit_
 template <int LEFT> __device__ __forceinline__ void copies_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(LEFT)); }
 
 // One level of a butterfly over COUNT values a lane: lanes whose bit OFFSET is set keep the upper half of the
-// values and hand over the lower half, the others the other way round; what stays is own + partner's. After the
+// values and hand over the lower half, the others the reverse; what stays is own + partner's. After the
 // levels 16, 8, 4, 2, 1 on 32 values lane l holds the sum over all lanes of value l. Every value's sum runs through
 // the same tree of lane pairs (l, l ^ 16), then (l, l ^ 8), ..., whatever its index: a sum does not depend on the
 // place of its token in a group.

@@ -99,15 +99,15 @@ def _zemozen(width, heads, kv_heads, dim, ff, vocab, layers, window, experts, th
     64 with states of 128 rows in 8 groups, four taps), every layer with routed experts whose `top` chosen ones
     together are as wide as the Llama shape's feed-forward, `through` of the router's outputs handing through."""
     attention = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "mask": {"size": window},
-                 "rot": {"base": 500000.0, "dims": dim, "scaling": {"factor": 8.0}}, "v_mix": True}
+                 "rot": {"base": 500000.0, "dims": dim, "scaling": {"factor": 4.0}}, "v_mix": True}
     left = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "mask": {"size": window},
-            "rot": {"base": 20000.0, "dims": dim}, "softcap": 30.0}
+            "rot": {"base": 10000.0, "dims": dim}, "softcap": 50.0}
     right = {"heads": width // 64, "groups": 8, "vdim": 64, "state": 128, "conv": 4, "norm_groups": 8}
     routed = {"kind": "moe", "router": {"experts": experts, "identity": through, "top": top}, "expert": {"ff": ff // top}}
     kinds = [{"type": "attention", "mixer": attention, "mlp": routed},
-             {"type": "parallel", "mixer": {"left": left, "right": right, "left_scale": 0.6, "right_scale": 0.9}, "mlp": routed}]
+             {"type": "parallel", "mixer": {"left": left, "right": right, "left_scale": 0.7, "right_scale": 1.1}, "mlp": routed}]
     return {"architecture": "Zemozen", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},
-            "residual_mult": 0.3, "layers": [kinds[i % 2] for i in range(layers)]}
+            "residual_mult": 0.5, "layers": [kinds[i % 2] for i in range(layers)]}
 
 
 # the layer sizes of llama-3.1-8b and llama-3.2-1b; windows of 2,048 unless a run sets another; 8 of 32 + 2 experts

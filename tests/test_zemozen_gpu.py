@@ -104,7 +104,7 @@ def _attention(fn, batch, heads, groups, dim, vdim, dtype, window, cap, unit, ga
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("case", [
     # heads, kv heads, head size, value size, window, soft cap, one in the denominator, head gate
-    (8, 1, 96, 64, 96, 30.0, True, False), (4, 1, 48, 48, 40, 0.0, False, True), (4, 2, 6, 10, 9, 1.5, True, False),
+    (8, 2, 96, 64, 80, 25.0, True, False), (6, 2, 48, 48, 50, 0.0, False, True), (4, 2, 6, 10, 9, 1.5, True, False),
     (8, 2, 32, 32, 130, 4.0, True, False), (2, 2, 128, 128, 70, 2.0, True, False), (4, 4, 96, 96, 0, 30.0, True, False),
     (4, 1, 64, 64, 40, 0.0, False, True), (2, 1, 128, 64, 100, 0.0, False, True), (16, 2, 64, 64, 1000, 0.7, True, True),
     (3, 3, 5, 300, 21, 3.0, False, True), (2, 1, 16, 24, 0, 0.0, True, False), (24, 2, 128, 128, 63, 5.0, True, False),
@@ -226,7 +226,7 @@ def _ssm(fn, proj, params, state, batch, H, G, N, V, dtype, parts=1, eps=1e-5, o
 
 
 # heads, groups, state, value size, taps, norm parts
-SSM_CASES = [(3, 1, 7, 5, 2, 3), (4, 2, 48, 48, 3, 2), (4, 2, 64, 32, 4, 1), (2, 2, 128, 64, 3, 2), (8, 1, 40, 16, 1, 4),
+SSM_CASES = [(3, 1, 7, 5, 2, 3), (4, 2, 48, 40, 3, 2), (4, 2, 64, 32, 4, 1), (2, 2, 128, 64, 3, 2), (8, 1, 40, 16, 1, 4),
              (2, 2, 20, 12, 4, 1), (1, 1, 256, 7, 2, 1), (6, 3, 33, 18, 5, 9), (2, 1, 130, 130, 2, 4)]
 
 
@@ -332,7 +332,7 @@ def _experts(fn, h, router, correction, w_up, w_down, top, pass_through, scale=0
 @pytest.mark.parametrize("case", [
     # width, expert width, experts with matrices, experts that hand through, chosen
     (40, 12, 5, 1, 3), (128, 64, 8, 2, 2), (128, 96, 4, 0, 1), (32, 16, 1, 2, 3), (256, 128, 16, 2, 4), (136, 40, 2, 5, 7),
-    (320, 96, 16, 2, 4), (64, 32, 3, 0, 3)])
+    (320, 104, 12, 2, 4), (64, 32, 3, 0, 3)])
 def test_routed_experts_scored_over_all_outputs(dtype, case):
     ops = _ops()
     hidden, F, E, through, top = case
@@ -473,7 +473,7 @@ def test_whole_decode_pieces_and_batches_agree_with_plain(tmp_path, which, dtype
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_long_decoding_passes_the_windows_and_page_edges(tmp_path, dtype):
-    """One token a step from the first on, 300 steps: windows of 40, 70, 100 and 130 slide over decoded tokens,
+    """One token a step from the first on, 300 steps: windows of 44, 70, 100 and 130 slide over decoded tokens,
     pages fill and follow each other, the recurrences' states are carried 300 times, values are blended with the
     first layer's step by step, and steps are replayed from graphs."""
     from llm_b200.engine import Entry
@@ -588,7 +588,7 @@ def test_what_a_fault_would_change_shows_in_the_logits(tmp_path):
         elif change == "norm parts":
             other["layers"][4]["mixer"]["right"]["norm_groups"] = 2
         elif change == "constant":
-            other["residual_mult"] = 0.41
+            other["residual_mult"] = 0.46
         elif change == "hand through":
             other["layers"][2]["mlp"]["router"]["identity"] = 0                     # the last output would be an expert with matrices
             other["layers"][2]["mlp"]["router"]["experts"] = 17

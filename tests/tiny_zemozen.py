@@ -70,17 +70,17 @@ ZEM_P = {
 # Q: sizes that tensor-core kernels take; windows narrower than a page and wider than two; attention first
 ZEM_Q = {
     "architecture": "Zemozen", "vocab": 320, "width": 128, "norm": {"eps": 1e-6}, "embedding": {"scale": 8.0},
-    "residual_mult": 0.4,
+    "residual_mult": 0.45,
     "layers": [
-        _layer("attention", _attention(4, 1, 64, 64, 40, rot={"base": 200000.0, "dims": 32, "scaling": {"factor": 8.0}}, v_mix=True),
+        _layer("attention", _attention(4, 1, 64, 64, 44, rot={"base": 200000.0, "dims": 32, "scaling": {"factor": 6.0}}, v_mix=True),
                _moe(8, 2, 2, 64)),
         _layer("parallel", _parallel(_attention(8, 2, 32, 32, 130, rot={"base": 5000.0, "dims": 32}, softcap=4.0),
-                                     _recurrence(4, 2, 32, 64, 4, 1), 0.6, 0.9), _moe(4, 0, 1, 96)),
+                                     _recurrence(4, 2, 32, 64, 4, 1), 0.65, 0.85), _moe(4, 0, 1, 96)),
         _layer("attention", _attention(2, 1, 128, 64, 100, rot={"base": 1000.0, "dims": 16}, scale=0.07, v_mix=True),
                _moe(16, 1, 4, 32)),
-        _layer("parallel", _parallel(_attention(2, 2, 128, 128, 70, rot={"base": 20000.0, "dims": 128}, scale=0.11, softcap=2.0),
+        _layer("parallel", _parallel(_attention(2, 2, 128, 128, 70, rot={"base": 30000.0, "dims": 128}, scale=0.11, softcap=2.0),
                                      _recurrence(2, 2, 64, 128, 3, 2), 1.2, 0.5), None),
-        _layer("parallel", _parallel(_attention(4, 4, 96, 96, 0, rot={"base": 300.0, "dims": 48}, softcap=30.0),
+        _layer("parallel", _parallel(_attention(4, 4, 96, 96, 0, rot={"base": 300.0, "dims": 48}, softcap=25.0),
                                      _recurrence(8, 1, 16, 40, 1, 4), 0.9, 1.1), _moe(6, 2, 3, 48)),
     ],
 }
